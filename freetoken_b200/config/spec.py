@@ -124,10 +124,16 @@ class ScheduleEntry:
     ``cache_from`` is ``None`` when the entry owns a cache of its own, else the index
     of an earlier schedule entry whose cache this entry's mixer reads (it then
     writes nothing).
+
+    What the model feeds into the stream right before the entry's layer (a repeated range of
+    layers starts each pass this way): ``add_embedding`` adds the tokens' input embedding once
+    more, ``add_pass_vector`` adds row ``i`` of the model's ``pass_vectors`` table to every token.
     """
 
     layer: int
     cache_from: Optional[int] = None
+    add_embedding: bool = False
+    add_pass_vector: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -145,6 +151,8 @@ class ModelSpec:
     embedding_name: str = "model.embed_tokens"
     final_norm_name: str = "model.norm"
     head_name: str = "lm_head"
+    pass_vectors: Optional[PartSpec] = None  # an embedding part with ``vector(i)`` (kind "pass_vectors")
+    pass_vectors_name: str = "pass_vectors"
     source: Any = None  # the architecture's own typed config, kept for reporting
 
     def validate(self) -> None:
@@ -163,3 +171,8 @@ class ModelSpec:
                     raise ConfigError(
                         f"schedule[{i}].cache_from={e.cache_from} names an entry that owns no cache"
                     )
+            if e.add_pass_vector is not None:
+                n_vec = int(self.pass_vectors["passes"]) if self.pass_vectors is not None else 0
+                if not 0 <= e.add_pass_vector < n_vec:
+                    raise ConfigError(f"schedule[{i}].add_pass_vector={e.add_pass_vector}, the model has "
+                                      f"{n_vec} pass vectors")

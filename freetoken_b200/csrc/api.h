@@ -27,7 +27,43 @@ typedef struct {
   const int32_t* slot_map;   // [T] slot = page * page_size + offset; negative skips the token
   int page_size;
   int num_pages;
+  const float* bias;         // [n_heads * head_dim] added to the projected heads first, or null
+  const float* pos_scale;    // [pos_scale_len] factor by the token's position, applied last, or null
+  int pos_scale_len;
+  int dst_head_dim;          // row length at the destination (>= head_dim; the rest is written as zeros); 0 = head_dim
 } FtkSection;
+
+// What ftk_stream_add_norm adds up and writes (see stream.cu).  Dense rows, routed rows and the table share `dtype`.
+typedef struct {
+  float* residual;           // [T, hidden] 32-bit stream; the sum is stored back unless `rows` is given
+  const void* x1;            // [T, hidden] or null
+  const void* x2;            // [T, hidden] or null
+  const void* y;             // [n_routes, hidden] routed rows or null: row t gets sum_j y[route_pos[t * top_k + j]]
+  const int32_t* route_pos;
+  int top_k;
+  int n_routes;
+  const void* table;         // [vocab, hidden] or null: row t gets table[ids[t]]
+  const int32_t* ids;
+  int vocab;
+  const float* vec;          // [hidden] added to every row, or null
+  int norm;                  // 0: out = the sum (or no out at all), 1: out = tanh(alpha z) * weight + bias
+  const float* weight;
+  const float* bias;
+  const float* alpha;        // one float on the device
+  void* out;                 // [n_rows, hidden] or null
+  int dtype;
+  const int32_t* rows;       // null, or the rows to take (out[i] belongs to rows[i]; the stream stays as it is)
+  int n_rows;
+  int hidden;
+} FtkStreamNorm;
+
+// Options of ftk_paged_attention_ex beyond ftk_paged_attention's.
+typedef struct {
+  // learned bias by distance: score(i, j) += dist_bias[head * dist_len + min(i - j, dist_len - 1)], not
+  // multiplied by `scale`; null = none
+  const float* dist_bias;
+  int dist_len;
+} FtkAttnExtras;
 
 const char* ftk_last_error(void);
 
@@ -42,6 +78,14 @@ int ftk_add_rmsnorm_routes(const void* y, int y_dtype, const int32_t* route_pos,
                            const void* shared, float* residual, const float* weight, void* out, int out_dtype,
                            float* out_f32, const int32_t* rows, int n_rows, int hidden, float eps, int gemma,
                            void* stream);
+int ftk_stream_add_norm(const FtkStreamNorm* args, void* stream);
+// o[t, h, :] *= sigmoid(gates[t * gate_stride + h]) in place; o [T, n_heads, head_dim]
+int ftk_head_gate(void* o, int dtype, const void* gates, long long gate_stride, int n_tokens, int n_heads,
+                  int head_dim, void* stream);
+// ids[t, j] = table[token_ids[t], j], weights[t, j] = weight: experts picked by a table over token ids
+int ftk_table_route(const int32_t* token_ids, const int32_t* table, int n_tokens, int vocab, int top_k,
+                    int n_experts, float weight, int32_t* ids, float* weights, void* stream);
+int ftk_scale_f32(float* x, long long n, float s, void* stream);
 int ftk_act_and_mul(const void* gate_up, int dtype, int n_rows, int inter, int act, float alpha,
                     float limit, void* out, void* stream);
 int ftk_cast(const void* src, int src_dtype, void* dst, int dst_dtype, long long n, void* stream);
@@ -57,6 +101,14 @@ int ftk_paged_attention(const void* q, const void* k_slab, const void* v_slab, i
                         const int32_t* items, int n_items, float* part_o, float* part_ml, int n_slots,
                         void* out, int n_q_heads, int n_kv_heads, int head_dim, int page_size,
                         int num_pages, int tile_rows, float scale, int window, void* stream);
+// The same with options (`extras` may be null).  k_slab == v_slab is allowed (values that are the keys): the
+// kernels then bring each key tile in once.
+int ftk_paged_attention_ex(const void* q, const void* k_slab, const void* v_slab, int dtype,
+                           const int32_t* block_table, int bt_stride, const int32_t* seg_info, int n_segs,
+                           const int32_t* items, int n_items, float* part_o, float* part_ml, int n_slots,
+                           void* out, int n_q_heads, int n_kv_heads, int head_dim, int page_size,
+                           int num_pages, int tile_rows, float scale, int window, const FtkAttnExtras* extras,
+                           void* stream);
 // Long steps in bfloat16 on tcgen05: tiles of 128 query rows (plan the items with tile_rows = 128), head
 // size 128, pages of a multiple of 16 tokens; n_tokens = rows of q.  ftk_attention_tc_fits says whether
 // the sizes are taken.

@@ -51,7 +51,18 @@ struct AttnParams {
   // decode tiles: one counter per (split tile, KV head), zero between launches; the last of a tile's
   // splits to arrive merges them, so no merge kernel follows.  nullptr: the merge kernel does it.
   unsigned int* arrivals;
+  // learned bias by distance, added to the scaled score: dist_bias[head * dist_len + min(i - j, dist_len - 1)]
+  // for query position i and key position j; nullptr: none
+  const float* dist_bias;
+  int dist_len;
 };
+
+// Bias of a key `dist` positions behind the query, from the row of the query's head (`row` may be null).
+__device__ __forceinline__ float dist_bias_at(const float* row, int dist_len, int dist) {
+  if (!row) return 0.f;
+  dist = dist < 0 ? 0 : (dist >= dist_len ? dist_len - 1 : dist);
+  return __ldg(row + dist);
+}
 
 constexpr int kAttnArrivalSlots = 1 << 16;
 __device__ unsigned int g_attn_arrivals[kAttnArrivalSlots];
@@ -123,6 +134,9 @@ __global__ void __launch_bounds__(kF32Rows * 32) attention_f32_kernel(AttnParams
   float* sq = smem;                       // [rows][D]
   float* sk = sq + kF32Rows * D;          // [chunk][D + 1]
   float* sv = sk + kF32Chunk * ldk;       // [chunk][D]
+  const bool tied = p.k == p.v;           // the values are the keys: one copy, read through the keys' rows
+  const float* svr = tied ? sk : sv;
+  const int ldv = tied ? ldk : D;
   __shared__ int spos[kF32Chunk];         // position in the sequence of each key of the chunk (-1: none)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int R = it.ntok * G;
@@ -138,6 +152,7 @@ __global__ void __launch_bounds__(kF32Rows * 32) attention_f32_kernel(AttnParams
   const bool active = warp < R;
   const int q_pos = it.kv_len - it.q_len + it.tok0 + warp / G;
   const int lo_row = p.window > 0 ? q_pos - p.window + 1 : 0;
+  const float* brow = (p.dist_bias && active) ? p.dist_bias + (size_t)(kvh * G + warp % G) * p.dist_len : nullptr;
   constexpr int kPer = 8;  // D <= 256
   float acc[kPer];
 #pragma unroll
@@ -154,12 +169,12 @@ __global__ void __launch_bounds__(kF32Rows * 32) attention_f32_kernel(AttnParams
         const long long off = kv_row_offset(p, it, kvh, c0 + j);
         if (off >= 0) {
           kval = to_float(kbase[off + d]);
-          vval = to_float(vbase[off + d]);
+          if (!tied) vval = to_float(vbase[off + d]);
         }
         if (d == 0) spos[j] = off >= 0 ? key_position(p, it, kvh, c0 + j) : -1;
       }
       sk[j * ldk + d] = kval;
-      sv[j * D + d] = vval;
+      if (!tied) sv[j * D + d] = vval;
     }
     __syncthreads();
     if (!active) continue;
@@ -171,7 +186,7 @@ __global__ void __launch_bounds__(kF32Rows * 32) attention_f32_kernel(AttnParams
       const float* kr = sk + lane * ldk;
       float dot = 0.f;
       for (int d = 0; d < D; ++d) dot = fmaf(qr[d], kr[d], dot);
-      s = dot * p.scale;
+      s = dot * p.scale + dist_bias_at(brow, p.dist_len, q_pos - key);
     }
     const float cm = warp_max(s);
     if (cm == -INFINITY) continue;  // nothing visible in this chunk
@@ -188,7 +203,7 @@ __global__ void __launch_bounds__(kF32Rows * 32) attention_f32_kernel(AttnParams
 #pragma unroll
         for (int i = 0; i < kPer; ++i) {
           const int d = lane + 32 * i;
-          if (d < D) acc[i] = fmaf(pb, sv[j * D + d], acc[i]);
+          if (d < D) acc[i] = fmaf(pb, svr[j * ldv + d], acc[i]);
         }
       }
     }
@@ -376,6 +391,7 @@ __device__ __forceinline__ void load_kv_tile(const AttnParams& p, const long lon
   const int chunks = p.D >> 3;
   const __nv_bfloat16* kb = (const __nv_bfloat16*)p.k;
   const __nv_bfloat16* vb = (const __nv_bfloat16*)p.v;
+  const bool tied = p.k == p.v;  // the values are the keys: the key tile serves both products
   if ((chunks & (chunks - 1)) == 0) {  // 2, 4, 8, 16 or 32 pieces per row
     const int c = threadIdx.x & (chunks - 1);
     const int step = 128 / chunks;
@@ -384,7 +400,7 @@ __device__ __forceinline__ void load_kv_tile(const AttnParams& p, const long lon
       const bool valid = off >= 0;
       const long long o = valid ? off + c * 8 : 0;
       cp_async16(sk + j * ld + c * 8, kb + o, valid);
-      cp_async16(sv + j * ld + c * 8, vb + o, valid);
+      if (!tied) cp_async16(sv + j * ld + c * 8, vb + o, valid);
     }
   } else {
     for (int i = threadIdx.x; i < kBN * chunks; i += blockDim.x) {
@@ -393,7 +409,7 @@ __device__ __forceinline__ void load_kv_tile(const AttnParams& p, const long lon
       const bool valid = off >= 0;
       const long long o = valid ? off + c * 8 : 0;
       cp_async16(sk + j * ld + c * 8, kb + o, valid);
-      cp_async16(sv + j * ld + c * 8, vb + o, valid);
+      if (!tied) cp_async16(sv + j * ld + c * 8, vb + o, valid);
     }
   }
 }
@@ -439,6 +455,10 @@ __global__ void __launch_bounds__(128) attention_bf16_kernel(AttnParams p) {
   const int lo0 = p.window > 0 ? qp0 - p.window + 1 : 0;
   const int lo1 = p.window > 0 ? qp1 - p.window + 1 : 0;
   const float sl2 = p.scale * 1.4426950408889634f;
+  const bool tied = p.k == p.v;
+  const float kLog2e = 1.4426950408889634f;
+  const float* brow0 = (p.dist_bias && r0 < R) ? p.dist_bias + (size_t)(kvh * G + r0 % G) * p.dist_len : nullptr;
+  const float* brow1 = (p.dist_bias && r1 < R) ? p.dist_bias + (size_t)(kvh * G + r1 % G) * p.dist_len : nullptr;
 
   float o[DMAX / 8][4];
 #pragma unroll
@@ -448,7 +468,7 @@ __global__ void __launch_bounds__(128) attention_bf16_kernel(AttnParams p) {
   for (int iter = 0; iter < n_iter; ++iter) {
     const int buf = iter & 1;
     __nv_bfloat16* sk = sk0 + buf * kBN * ld;
-    __nv_bfloat16* sv = sv0 + buf * kBN * ld;
+    __nv_bfloat16* sv = tied ? sk : sv0 + buf * kBN * ld;
     if (iter + 1 < n_iter)
       load_kv_tile(p, row_off[(iter + 1) % 3], sk0 + (buf ^ 1) * kBN * ld, sv0 + (buf ^ 1) * kBN * ld, ld);
     cp_async_commit();
@@ -486,8 +506,8 @@ __global__ void __launch_bounds__(128) attention_bf16_kernel(AttnParams p) {
         const bool in = key < it.ke;
         const bool v0 = in && key <= qp0 && key >= lo0;
         const bool v1 = in && key <= qp1 && key >= lo1;
-        s[n][e] = v0 ? s[n][e] * sl2 : -INFINITY;
-        s[n][2 + e] = v1 ? s[n][2 + e] * sl2 : -INFINITY;
+        s[n][e] = v0 ? s[n][e] * sl2 + dist_bias_at(brow0, p.dist_len, qp0 - key) * kLog2e : -INFINITY;
+        s[n][2 + e] = v1 ? s[n][2 + e] * sl2 + dist_bias_at(brow1, p.dist_len, qp1 - key) * kLog2e : -INFINITY;
         mx0 = fmaxf(mx0, s[n][e]);
         mx1 = fmaxf(mx1, s[n][2 + e]);
       }
@@ -693,6 +713,10 @@ __global__ void __launch_bounds__(128) attention_decode_bf16_kernel(AttnParams p
   const int lo0 = p.window > 0 ? qp0 - p.window + 1 : 0;
   const int lo1 = p.window > 0 ? qp1 - p.window + 1 : 0;
   const float sl2 = p.scale * 1.4426950408889634f;
+  const bool tied = p.k == p.v;
+  const float kLog2e = 1.4426950408889634f;
+  const float* brow0 = (p.dist_bias && r0 < R) ? p.dist_bias + (size_t)(kvh * G + r0 % G) * p.dist_len : nullptr;
+  const float* brow1 = (p.dist_bias && r1 < R) ? p.dist_bias + (size_t)(kvh * G + r1 % G) * p.dist_len : nullptr;
 
   float o[DMAX / 8][4];
 #pragma unroll
@@ -710,7 +734,7 @@ __global__ void __launch_bounds__(128) attention_decode_bf16_kernel(AttnParams p
     const long long next_off = fetch_row_offset(p, it, kvh, it.kb + (iter + 3) * kBN);
     const int stage = iter % kDecStages;
     const __nv_bfloat16* sk = sk0 + stage * kBN * ld + warp * 16 * ld;  // this warp's 16 keys
-    const __nv_bfloat16* sv = sv0 + stage * kBN * ld + warp * 16 * ld;
+    const __nv_bfloat16* sv = tied ? sk : sv0 + stage * kBN * ld + warp * 16 * ld;
 
     float s[2][4];
     s[0][0] = s[0][1] = s[0][2] = s[0][3] = s[1][0] = s[1][1] = s[1][2] = s[1][3] = 0.f;
@@ -728,7 +752,7 @@ __global__ void __launch_bounds__(128) attention_decode_bf16_kernel(AttnParams p
     float mx0 = -INFINITY, mx1 = -INFINITY;
     // a 16-key slice that every row of the tile may read in full needs no mask (rows beyond the
     // tile's last are never stored, so what they compute does not matter)
-    const bool interior = p.window == 0 && !p.sel && c0 + 16 <= it.ke && c0 + 16 <= pos_base + 1;
+    const bool interior = p.window == 0 && !p.sel && !p.dist_bias && c0 + 16 <= it.ke && c0 + 16 <= pos_base + 1;
     if (interior) {
 #pragma unroll
       for (int n = 0; n < 2; ++n) {
@@ -748,8 +772,8 @@ __global__ void __launch_bounds__(128) attention_decode_bf16_kernel(AttnParams p
           if (p.sel) key = in ? row_pos[iter & 3][warp * 16 + col] : -1;
           const bool v0 = in && key >= 0 && key <= qp0 && key >= lo0;
           const bool v1 = in && key >= 0 && key <= qp1 && key >= lo1;
-          s[n][e] = v0 ? s[n][e] * sl2 : -INFINITY;
-          s[n][2 + e] = v1 ? s[n][2 + e] * sl2 : -INFINITY;
+          s[n][e] = v0 ? s[n][e] * sl2 + dist_bias_at(brow0, p.dist_len, qp0 - key) * kLog2e : -INFINITY;
+          s[n][2 + e] = v1 ? s[n][2 + e] * sl2 + dist_bias_at(brow1, p.dist_len, qp1 - key) * kLog2e : -INFINITY;
           mx0 = fmaxf(mx0, s[n][e]);
           mx1 = fmaxf(mx1, s[n][2 + e]);
         }
@@ -955,6 +979,7 @@ static int paged_attention_tc_impl(const void* q, const void* k_slab, const void
   p.Hq = n_q_heads; p.Hkv = n_kv_heads; p.G = n_q_heads / n_kv_heads; p.D = head_dim; p.P = page_size;
   p.num_pages = num_pages; p.tile_rows = pair ? 2 * kTcRows : few ? kTcFewRows : kTcRows; p.scale = scale; p.window = window;
   p.sel = nullptr; p.sel_stride = 0; p.block_size = 0; p.arrivals = nullptr;
+  p.dist_bias = nullptr; p.dist_len = 0;
   cudaStream_t s = (cudaStream_t)stream;
   note_variant(pair ? "attention: tcgen05, two 128-row query tiles per CTA"
                : few ? "attention: tcgen05, tiles of at most 16 rows, one softmax warp"
@@ -1011,7 +1036,8 @@ static int paged_attention_impl(const void* q, const void* k_slab, const void* v
                                 int n_segs, const int32_t* items, int n_items, float* part_o,
                                 float* part_ml, int n_slots, void* out, int n_q_heads, int n_kv_heads,
                                 int head_dim, int page_size, int num_pages, int tile_rows, float scale,
-                                int window, const int32_t* sel, int sel_stride, int block_size, void* stream) {
+                                int window, const int32_t* sel, int sel_stride, int block_size, void* stream,
+                                const FtkAttnExtras* extras = nullptr) {
   FTK_REQUIRE(dtype_ok(dtype), "paged_attention: bad dtype %d", dtype);
   FTK_REQUIRE(n_items >= 0 && n_segs >= 0, "paged_attention: bad counts");
   if (n_items == 0) return 0;
@@ -1032,6 +1058,10 @@ static int paged_attention_impl(const void* q, const void* k_slab, const void* v
   p.num_pages = num_pages; p.tile_rows = tile_rows; p.scale = scale; p.window = window;
   p.sel = sel; p.sel_stride = sel_stride; p.block_size = block_size;
   p.arrivals = nullptr;
+  p.dist_bias = extras ? extras->dist_bias : nullptr;
+  p.dist_len = extras ? extras->dist_len : 0;
+  FTK_REQUIRE(!p.dist_bias || p.dist_len >= 1, "paged_attention: a distance bias needs at least one entry per head");
+  FTK_REQUIRE(!p.dist_bias || !sel, "paged_attention: a distance bias cannot be combined with block selection");
   if (sel) {
     FTK_REQUIRE(sel_stride >= 1 && block_size >= 1, "paged_attention: bad block selection geometry");
     FTK_REQUIRE(window == 0, "paged_attention: a window cannot be combined with block selection");
@@ -1104,6 +1134,17 @@ extern "C" int ftk_paged_attention(const void* q, const void* k_slab, const void
   return paged_attention_impl(q, k_slab, v_slab, dtype, block_table, bt_stride, seg_info, n_segs, items, n_items, part_o,
                               part_ml, n_slots, out, n_q_heads, n_kv_heads, head_dim, page_size, num_pages, tile_rows,
                               scale, window, nullptr, 0, 0, stream);
+}
+
+extern "C" int ftk_paged_attention_ex(const void* q, const void* k_slab, const void* v_slab, int dtype,
+                                      const int32_t* block_table, int bt_stride, const int32_t* seg_info,
+                                      int n_segs, const int32_t* items, int n_items, float* part_o,
+                                      float* part_ml, int n_slots, void* out, int n_q_heads, int n_kv_heads,
+                                      int head_dim, int page_size, int num_pages, int tile_rows, float scale,
+                                      int window, const FtkAttnExtras* extras, void* stream) {
+  return paged_attention_impl(q, k_slab, v_slab, dtype, block_table, bt_stride, seg_info, n_segs, items, n_items, part_o,
+                              part_ml, n_slots, out, n_q_heads, n_kv_heads, head_dim, page_size, num_pages, tile_rows,
+                              scale, window, nullptr, 0, 0, stream, extras);
 }
 
 // Block-sparse layers: `sel [T, n_kv_heads, sel_stride]` lists, per token and KV head, the chosen key

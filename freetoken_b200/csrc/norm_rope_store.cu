@@ -10,6 +10,12 @@
 // memory so that a lane can read its rotation partner, rotated with the cos/sin row of the token's
 // position, and written to its destination: a dense [T, heads, D] tensor (queries) or the row of a
 // paged slab [pages, heads, page_size, D] that the token's slot names (keys, values).
+//
+// A section may also add a bias to its heads first (projections whose bias is not added by the matrix
+// product), multiply them last by a factor that depends on the token's position (a query temperature
+// that grows with the position, say) and write rows that are longer than the head (zero-filled: head
+// sizes the attention kernels do not take are padded to the next one they do).  Norm, rotation, bias and
+// factor are each optional, so attention without rotation uses the same kernel.
 #include "common.cuh"
 
 namespace ftk {
@@ -52,10 +58,11 @@ __global__ void norm_rope_store_kernel(const T* __restrict__ x, int n_tokens, in
   constexpr int kPer = kMaxHeadDim / 32;
   float v[kPer];
   float ss = 0.f;
+  const float* bias = S.bias ? S.bias + (size_t)hl * head_dim : nullptr;
 #pragma unroll
   for (int i = 0; i < kPer; ++i) {
     const int d = lane + 32 * i;
-    v[i] = d < head_dim ? to_float(src[d]) : 0.f;
+    v[i] = d < head_dim ? to_float(src[d]) + (bias ? bias[d] : 0.f) : 0.f;
     ss += v[i] * v[i];
   }
   if (S.norm_weight) {
@@ -89,17 +96,25 @@ __global__ void norm_rope_store_kernel(const T* __restrict__ x, int n_tokens, in
       }
     }
   }
+  if (S.pos_scale) {
+    int pos = positions[t];
+    pos = pos < 0 ? 0 : (pos >= S.pos_scale_len ? S.pos_scale_len - 1 : pos);
+    const float f = S.pos_scale[pos];
+#pragma unroll
+    for (int i = 0; i < kPer; ++i) v[i] *= f;
+  }
+  const int dst_dim = S.dst_head_dim > 0 ? S.dst_head_dim : head_dim;
   T* dst;
   if (S.slab) {
     const long long page = slot / S.page_size, off = slot % S.page_size;
-    dst = (T*)S.slab + (((size_t)page * S.n_heads + hl) * S.page_size + off) * head_dim;
+    dst = (T*)S.slab + (((size_t)page * S.n_heads + hl) * S.page_size + off) * dst_dim;
   } else {
-    dst = (T*)S.dense_out + ((size_t)t * S.n_heads + hl) * head_dim;
+    dst = (T*)S.dense_out + ((size_t)t * S.n_heads + hl) * dst_dim;
   }
 #pragma unroll
   for (int i = 0; i < kPer; ++i) {
     const int d = lane + 32 * i;
-    if (d < head_dim) dst[d] = from_float<T>(v[i]);
+    if (d < dst_dim) dst[d] = from_float<T>(d < head_dim ? v[i] : 0.f);
   }
 }
 
@@ -158,6 +173,12 @@ norm_rope_store_vec_kernel(const __nv_bfloat16* __restrict__ x, int n_tokens, in
     *reinterpret_cast<float4*>(cb) = *reinterpret_cast<const float4*>(b);
     *reinterpret_cast<float4*>(cb + 4) = *reinterpret_cast<const float4*>(b + 4);
   }
+  float factor = 1.f;
+  if (S.pos_scale) {
+    int pos = positions[t];
+    pos = pos < 0 ? 0 : (pos >= S.pos_scale_len ? S.pos_scale_len - 1 : pos);
+    factor = S.pos_scale[pos];
+  }
   float v[8];
   {
     uint4 raw = make_uint4(0u, 0u, 0u, 0u);
@@ -168,6 +189,14 @@ norm_rope_store_vec_kernel(const __nv_bfloat16* __restrict__ x, int n_tokens, in
       const float2 f = __bfloat1622float2(h2[j]);
       v[2 * j] = f.x;
       v[2 * j + 1] = f.y;
+    }
+    if (S.bias && live) {
+      float b[8];
+      const float* bp = S.bias + (size_t)hl * kHeadDim + l * 8;
+      *reinterpret_cast<float4*>(b) = *reinterpret_cast<const float4*>(bp);
+      *reinterpret_cast<float4*>(b + 4) = *reinterpret_cast<const float4*>(bp + 4);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] += b[j];
     }
   }
   {
@@ -204,6 +233,10 @@ norm_rope_store_vec_kernel(const __nv_bfloat16* __restrict__ x, int n_tokens, in
 #pragma unroll
       for (int j = 0; j < 8; ++j) v[j] = low ? v[j] * ca[j] - partner[j] * cb[j] : v[j] * ca[j] + partner[j] * cb[j];
     }
+  }
+  if (S.pos_scale) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] *= factor;
   }
   if (!store) return;
   __nv_bfloat16* dst;
@@ -252,6 +285,9 @@ extern "C" int ftk_norm_rope_store(const void* x, int dtype, int n_tokens, int r
     FTK_REQUIRE((S.dense_out != nullptr) != (S.slab != nullptr),
                 "norm_rope_store: section %d needs exactly one destination", i);
     if (S.slab) FTK_REQUIRE(S.slot_map && S.page_size >= 1 && S.num_pages >= 1, "norm_rope_store: section %d has a bad slab", i);
+    FTK_REQUIRE(!S.pos_scale || (positions && S.pos_scale_len >= 1), "norm_rope_store: section %d scales by position without positions or table", i);
+    FTK_REQUIRE(S.dst_head_dim == 0 || (S.dst_head_dim >= head_dim && S.dst_head_dim <= kMaxHeadDim),
+                "norm_rope_store: section %d writes rows of %d for heads of %d", i, S.dst_head_dim, head_dim);
     any_rot = any_rot || S.rotate;
     sec.total_heads += S.n_heads;
   }
@@ -263,7 +299,9 @@ extern "C" int ftk_norm_rope_store(const void* x, int dtype, int n_tokens, int r
              row_elems % 8 == 0 && ((uintptr_t)x & 15) == 0;
   for (int i = 0; i < n_sections && vec; ++i) {
     const FtkSection& S = sections[i];
-    if (((uintptr_t)S.dense_out & 15) || ((uintptr_t)S.slab & 15) || ((uintptr_t)S.norm_weight & 15)) vec = false;
+    if (((uintptr_t)S.dense_out & 15) || ((uintptr_t)S.slab & 15) || ((uintptr_t)S.norm_weight & 15) ||
+        ((uintptr_t)S.bias & 15) || (S.dst_head_dim != 0 && S.dst_head_dim != head_dim))
+      vec = false;
   }
   const int bx = (sec.total_heads + kWarpsPerBlock - 1) / kWarpsPerBlock;
   for (int t0 = 0; t0 < n_tokens; t0 += 65535) {
@@ -271,7 +309,8 @@ extern "C" int ftk_norm_rope_store(const void* x, int dtype, int n_tokens, int r
     Sections part = sec;
     for (int i = 0; i < n_sections; ++i) {
       if (part.s[i].dense_out)
-        part.s[i].dense_out = (char*)part.s[i].dense_out + (size_t)t0 * part.s[i].n_heads * head_dim * dtype_size(dtype);
+        part.s[i].dense_out = (char*)part.s[i].dense_out +
+                              (size_t)t0 * part.s[i].n_heads * (part.s[i].dst_head_dim ? part.s[i].dst_head_dim : head_dim) * dtype_size(dtype);
       if (part.s[i].slot_map) part.s[i].slot_map += t0;
     }
     dim3 grid(bx, nt);

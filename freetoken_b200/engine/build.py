@@ -7,6 +7,7 @@ the folder's safetensors files or with seeded random tensors made on the device.
 
 from __future__ import annotations
 
+import os
 from typing import Any, Dict, Mapping, Optional, Tuple
 
 import torch
@@ -16,6 +17,7 @@ from ..models.model import Model
 from ..parts import BuildEnv, Workspace
 from ..registry import Architecture, architecture_of
 from ..weights.binder import bind_folder
+from ..weights.safetensors_io import ModelFolder
 from ..weights.random_init import random_tensors_on_device
 
 
@@ -30,6 +32,19 @@ def describe_model(raw_config: Mapping[str, Any], num_layers: Optional[int] = No
     env = BuildEnv(dtype=torch.bfloat16, device=cpu, max_seq_len=1, max_step_tokens=1,
                    workspace=Workspace(cpu))
     return arch, typed, spec, Model(spec, env).param_specs()
+
+
+def typed_config(arch: Architecture, raw_config: Mapping[str, Any], folder: Optional[str] = None,
+                 num_layers: Optional[int] = None) -> Any:
+    """The architecture's typed config of a config.json; where the architecture takes sizes from the
+    shapes of the checkpoint's tensors (``Architecture.sizes_from_weights``) and ``folder`` holds weight
+    files, their headers are read for them."""
+    typed = arch.parse_config(raw_config, num_layers=num_layers)
+    if arch.sizes_from_weights is not None and folder and os.path.isdir(folder) \
+            and any(f.endswith(".safetensors") for f in os.listdir(folder)):
+        mf = ModelFolder(folder)
+        typed = arch.sizes_from_weights(typed, {n: tuple(mf.shape(n)) for n in mf.names()})
+    return typed
 
 
 def build_model(spec: ModelSpec, env: BuildEnv) -> Model:

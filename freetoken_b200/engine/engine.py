@@ -33,7 +33,7 @@ from ..errors import CacheError, ConfigError, SchedulerError
 from ..kernels import ops
 from ..parts import BuildEnv, PositionEncoding, Segment, StepState, Workspace
 from ..registry import architecture_of
-from .build import build_model, load_weights, random_weights
+from .build import build_model, load_weights, random_weights, typed_config
 from .step import StepBuffers, StepBuilder
 
 _TORCH_DTYPE = {"bfloat16": torch.bfloat16, "float32": torch.float32}
@@ -75,7 +75,8 @@ class Engine:
             raw = read_config_json(config.model_path)
         if raw is not None:
             self.arch = architecture_of(raw)
-            self.typed = self.arch.parse_config(raw, num_layers=config.num_layers)
+            self.typed = typed_config(self.arch, raw, None if config.use_dummy_weight else config.model_path,
+                                      config.num_layers)
         if spec is None:
             if self.arch is None:
                 raise ConfigError(f"{config.model_path}: no config.json in the model folder")
@@ -121,6 +122,9 @@ class Engine:
             table = getattr(part, "table", None)
             if callable(table) and isinstance(part, PositionEncoding):
                 table()
+                factors = getattr(part, "scale_table", None)
+                if callable(factors):
+                    factors()
 
         itemsize = 4 if self.dtype == torch.float32 else 2
         if config.num_page_override is not None:

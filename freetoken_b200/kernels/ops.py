@@ -25,6 +25,10 @@ add_rmsnorm_routes     moe_combine + add_rmsnorm in one pass
 linear                 python/freetoken/layers/linear.py:66-70 (the library product)
 copy_tokens            the sampled tokens of the step before, taken on the device
                        (python/freetoken/scheduler/scheduler.py:194-256, overlapped scheduling)
+stream_add_norm        no counterpart: several addends into the 32-bit stream and a norm without
+                       row statistics (Dynamic Tanh) in one pass
+head_gate, table_route, scale  no counterpart: per-head output gate, experts by a table over
+                       token ids, logit scale
 =====================  ==========================================================
 
 ``paged_attention`` runs one of five kernels by ``tile_rows``: 16 (float32, or bfloat16 steps of single
@@ -57,7 +61,20 @@ class _Section(ctypes.Structure):
     _fields_ = [
         ("first_head", _i), ("n_heads", _i), ("norm_weight", _vp), ("rotate", _i),
         ("dense_out", _vp), ("slab", _vp), ("slot_map", _vp), ("page_size", _i), ("num_pages", _i),
+        ("bias", _vp), ("pos_scale", _vp), ("pos_scale_len", _i), ("dst_head_dim", _i),
     ]
+
+
+class _StreamNorm(ctypes.Structure):
+    _fields_ = [
+        ("residual", _vp), ("x1", _vp), ("x2", _vp), ("y", _vp), ("route_pos", _vp), ("top_k", _i), ("n_routes", _i),
+        ("table", _vp), ("ids", _vp), ("vocab", _i), ("vec", _vp), ("norm", _i), ("weight", _vp), ("bias", _vp),
+        ("alpha", _vp), ("out", _vp), ("dtype", _i), ("rows", _vp), ("n_rows", _i), ("hidden", _i),
+    ]
+
+
+class _AttnExtras(ctypes.Structure):
+    _fields_ = [("dist_bias", _vp), ("dist_len", _i)]
 
 
 _SIGNATURES = {
@@ -68,6 +85,12 @@ _SIGNATURES = {
                             ctypes.POINTER(_Section), _vp],
     "ftk_paged_attention": [_vp, _vp, _vp, _i, _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _i, _vp,
                             _i, _i, _i, _i, _i, _i, _f, _i, _vp],
+    "ftk_paged_attention_ex": [_vp, _vp, _vp, _i, _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _i, _vp,
+                               _i, _i, _i, _i, _i, _i, _f, _i, ctypes.POINTER(_AttnExtras), _vp],
+    "ftk_stream_add_norm": [ctypes.POINTER(_StreamNorm), _vp],
+    "ftk_head_gate": [_vp, _i, _vp, ctypes.c_longlong, _i, _i, _i, _vp],
+    "ftk_table_route": [_vp, _vp, _i, _i, _i, _i, _f, _vp, _vp, _vp],
+    "ftk_scale_f32": [_vp, ctypes.c_longlong, _f, _vp],
     "ftk_attention_tc_fits": [_i, _i, _i],
     "ftk_paged_attention_tc": [_vp, _vp, _vp, _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _i, _vp,
                                _i, _i, _i, _i, _i, _i, _f, _i, _vp],
@@ -326,6 +349,11 @@ def norm_rope_store(x: torch.Tensor, head_dim: int, rotary_dim: int, positions: 
     ``slab [pages, n_heads, page_size, head_dim]`` with ``slot_map [T]`` (slot = page *
     page_size + offset, negative = skip).  ``rope_table [max_pos, rotary_dim]`` holds
     cos then sin of ``position * inv_freq`` in float32.
+
+    Optional keys of a section: ``bias`` (float32 ``[n_heads * head_dim]``, added first),
+    ``pos_scale`` (float32 ``[positions]``, the heads are multiplied last by the entry of the
+    token's position), ``dst_head_dim`` (the destination's rows are that long, zero-filled past
+    ``head_dim``).
     """
     T = x.shape[0]
     n_total = x.shape[1] // head_dim
@@ -341,13 +369,21 @@ def norm_rope_store(x: torch.Tensor, head_dim: int, rotary_dim: int, positions: 
         dense, slab = s.get("dense_out"), s.get("slab")
         if (dense is None) == (slab is None):
             raise KernelError("norm_rope_store: a section needs exactly one of dense_out and slab")
+        dst_dim = int(s.get("dst_head_dim") or head_dim)
+        arr[i].dst_head_dim = dst_dim if dst_dim != head_dim else 0
+        bias, pos_scale = s.get("bias"), s.get("pos_scale")
+        if bias is not None and bias.numel() != s["n_heads"] * head_dim:
+            raise KernelError("norm_rope_store: a section's bias must hold n_heads * head_dim entries")
+        arr[i].bias = _dev(bias, "bias", torch.float32)
+        arr[i].pos_scale = _dev(pos_scale, "pos_scale", torch.float32)
+        arr[i].pos_scale_len = pos_scale.numel() if pos_scale is not None else 0
         if dense is not None:
-            if dense.dtype != x.dtype or dense.numel() != T * s["n_heads"] * head_dim:
+            if dense.dtype != x.dtype or dense.numel() != T * s["n_heads"] * dst_dim:
                 raise KernelError("norm_rope_store: dense_out has the wrong dtype or size")
             arr[i].dense_out = _dev(dense, "dense_out")
         else:
             if slab.dtype != x.dtype or slab.dim() != 4 or slab.shape[1] != s["n_heads"] \
-                    or slab.shape[3] != head_dim:
+                    or slab.shape[3] != dst_dim:
                 raise KernelError("norm_rope_store: slab must be [pages, n_heads, page_size, head_dim]")
             arr[i].slab = _dev(slab, "slab")
             arr[i].slot_map = _dev(s["slot_map"], "slot_map", torch.int32)
@@ -372,7 +408,7 @@ def paged_attention(q: torch.Tensor, k_slab: torch.Tensor, v_slab: torch.Tensor,
                     items: torch.Tensor, n_items: int, part_o: Optional[torch.Tensor],
                     part_ml: Optional[torch.Tensor], out: torch.Tensor, tile_rows: int, scale: float,
                     window: Optional[int], sel: Optional[torch.Tensor] = None, block_size: int = 0,
-                    few_rows: bool = False) -> None:
+                    few_rows: bool = False, dist_bias: Optional[torch.Tensor] = None) -> None:
     """Causal softmax attention of the step's queries over the paged keys and values.
 
     ``q, out [T, Hq, D]``; slabs ``[pages, Hkv, page_size, D]``; ``block_table [rows, width]``
@@ -390,6 +426,11 @@ def paged_attention(q: torch.Tensor, k_slab: torch.Tensor, v_slab: torch.Tensor,
     ``few_rows`` (with ``tile_rows = 16``, bfloat16) runs the tcgen05 kernel in its form for decode
     steps (one warp takes the softmax of a tile's at most 16 rows); its work list has key pieces that
     are multiples of 128 (``build_plan(..., key_tile=128)``).
+
+    ``dist_bias [Hq, L]`` (float32) adds ``dist_bias[h, min(i - j, L - 1)]`` to the scaled score of query
+    position ``i`` and key position ``j`` (a learned bias by distance; not multiplied by ``scale``).
+    ``v_slab`` may be ``k_slab`` itself (values that are the keys): each key tile is then brought in once.
+    The tcgen05 kernels take neither.
     """
     T, Hq, D = q.shape
     pages, Hkv, P, D2 = k_slab.shape
@@ -405,8 +446,9 @@ def paged_attention(q: torch.Tensor, k_slab: torch.Tensor, v_slab: torch.Tensor,
         raise KernelError(f"paged_attention: few_rows goes with tiles of 16 rows, got {tile_rows}")
     if tile_rows in (128, 256) or few_rows:
         # bfloat16 steps on the tcgen05 kernels: one query tile per CTA, a pair of them, or tiles of a few rows
-        if sel is not None or window or q.dtype != torch.bfloat16:
-            raise KernelError("paged_attention: the tcgen05 kernels take bfloat16 without window or block selection")
+        if sel is not None or window or q.dtype != torch.bfloat16 or dist_bias is not None:
+            raise KernelError("paged_attention: the tcgen05 kernels take bfloat16 without window, block selection "
+                              "or distance bias")
         fn = (_lib().ftk_paged_attention_tc_few if few_rows else
               _lib().ftk_paged_attention_tc_pair if tile_rows == 256 else _lib().ftk_paged_attention_tc)
         _check(fn(
@@ -430,6 +472,20 @@ def paged_attention(q: torch.Tensor, k_slab: torch.Tensor, v_slab: torch.Tensor,
             _dev(out, "out"), Hq, Hkv, D, P, pages, tile_rows, float(scale),
             _dev(sel, "sel", torch.int32), sel.shape[2], int(block_size), _stream()),
             "paged_attention (block-sparse)", 2 if n_slots else 1)
+        return
+    if dist_bias is not None:
+        if dist_bias.dim() != 2 or dist_bias.shape[0] != Hq or dist_bias.shape[1] < 1:
+            raise KernelError("paged_attention: dist_bias must be [Hq, L]")
+        ex = _AttnExtras(_dev(dist_bias, "dist_bias", torch.float32), dist_bias.shape[1])
+        _check(_lib().ftk_paged_attention_ex(
+            _dev(q, "q"), _dev(k_slab, "k_slab"), _dev(v_slab, "v_slab"), _code(q, "q"),
+            _dev(block_table, "block_table", torch.int32), block_table.shape[1],
+            _dev(seg_info, "seg_info", torch.int32), n_segs,
+            _dev(items, "items", torch.int32), n_items,
+            _dev(part_o, "part_o", torch.float32), _dev(part_ml, "part_ml", torch.float32), n_slots,
+            _dev(out, "out"), Hq, Hkv, D, P, pages, tile_rows, float(scale),
+            int(window) if window else 0, ctypes.byref(ex), _stream()), "paged_attention (distance bias)",
+            2 if n_slots else 1)
         return
     _check(_lib().ftk_paged_attention(
         _dev(q, "q"), _dev(k_slab, "k_slab"), _dev(v_slab, "v_slab"), _code(q, "q"),
@@ -558,7 +614,7 @@ def small_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     _check(_lib().ftk_small_linear(_dev(x, "x"), _dev(w, "w"), _dev(out, "out"), T, N, K, _stream()), "small_linear")
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None) -> None:
     """``out = x @ w^T`` (``x [T, K]``, ``w [N, K]``, ``out [T, N]``): by the library, as in the reference
     (python/freetoken/layers/linear.py:66-70), except for bfloat16 steps of up to four tokens, whose
     product is a stream over the weights that :func:`small_linear` does faster than the library's choice
@@ -572,6 +628,11 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     N = w.shape[0]
     if w.shape != (N, K) or out.shape != (T, N):
         raise KernelError("linear: shapes do not agree")
+    if bias is not None:  # ``out = x @ w^T + bias``: the bias is added to the 32-bit sums by the library's product
+        if bias.shape != (N,) or bias.dtype != x.dtype:
+            raise KernelError("linear: bias must be [N] of x's dtype")
+        torch.addmm(bias, x, w.t(), out=out)
+        return
     if (T <= SMALL_LINEAR_MAX_TOKENS and x.dtype == torch.bfloat16 and x.is_cuda and x.is_contiguous()
             and w.is_contiguous() and out.is_contiguous() and small_linear_fits(T, N, K)):
         small_linear(x, w, out)
@@ -756,3 +817,90 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
                              _dev(top_k, "top_k", torch.int32), _dev(top_p, "top_p", torch.float32),
                              _dev(u, "u", torch.float32), _dev(out, "out", torch.int32), _stream()),
            "sample")
+
+
+# --------------------------------------------------------------------------- the 32-bit stream
+NORM_NONE, NORM_DYNAMIC_TANH = 0, 1
+
+
+def stream_add_norm(residual: Optional[torch.Tensor], out: Optional[torch.Tensor], x1: Optional[torch.Tensor] = None,
+                    x2: Optional[torch.Tensor] = None, routed: Optional[tuple] = None, table: Optional[torch.Tensor] = None,
+                    ids: Optional[torch.Tensor] = None, vec: Optional[torch.Tensor] = None,
+                    norm: Optional[tuple] = None, rows: Optional[torch.Tensor] = None) -> None:
+    """Several addends into the 32-bit stream and a norm without row statistics, in one pass.
+
+    ``z[t] = residual[t] + x1[t] + x2[t] + sum_j y[route_pos[t k + j]] + table[ids[t]] + vec`` with every
+    sum in 32 bits (each addend may be None; ``routed = (y, route_pos, top_k)``); without ``rows`` ``z`` is
+    stored back to ``residual``.  ``norm = ("dynamic_tanh", weight, bias, alpha)`` (float32 ``[H]``, ``[H]``
+    and one element) writes ``out = tanh(alpha z) weight + bias``; ``norm = None`` writes ``out = z`` when
+    ``out`` is given.  With ``rows`` only those rows are taken and ``out[i]`` belongs to ``rows[i]``."""
+    src = next((t for t in (residual, x1, x2, out) if t is not None), None)
+    if src is None:
+        raise KernelError("stream_add_norm: nothing to work on")
+    H = src.shape[-1]
+    total = (residual if residual is not None else src).numel() // H
+    n_rows = rows.shape[0] if rows is not None else total
+    a = _StreamNorm()
+    dense = [t for t in (x1, x2, routed[0] if routed else None, table, out) if t is not None]
+    dt = dense[0].dtype if dense else torch.float32
+    if any(t.dtype != dt for t in dense):
+        raise KernelError("stream_add_norm: addends, table and out must share one dtype")
+    a.residual = _dev(residual, "residual", torch.float32)
+    for name, t in (("x1", x1), ("x2", x2)):
+        if t is not None and t.numel() != total * H:
+            raise KernelError(f"stream_add_norm: {name} must be [tokens, hidden]")
+        setattr(a, name, _dev(t, name))
+    if routed is not None:
+        y, pos, top_k = routed
+        if y.dim() != 2 or y.shape[1] != H or pos.numel() != total * top_k:
+            raise KernelError("stream_add_norm: routed rows / positions have the wrong shape")
+        a.y, a.route_pos, a.top_k, a.n_routes = _dev(y, "y"), _dev(pos, "route_pos", torch.int32), int(top_k), y.shape[0]
+    if table is not None:
+        if ids is None or ids.numel() < total or table.dim() != 2 or table.shape[1] != H:
+            raise KernelError("stream_add_norm: a table needs [vocab, hidden] rows and one id per token")
+        a.table, a.ids, a.vocab = _dev(table, "table"), _dev(ids, "ids", torch.int32), table.shape[0]
+    if vec is not None:
+        if vec.numel() != H:
+            raise KernelError("stream_add_norm: vec must hold hidden entries")
+        a.vec = _dev(vec, "vec", torch.float32)
+    if norm is not None:
+        kind, w, b, alpha = norm
+        if kind != "dynamic_tanh" or w.shape != (H,) or b.shape != (H,) or alpha.numel() != 1 or out is None:
+            raise KernelError("stream_add_norm: norm must be ('dynamic_tanh', weight [H], bias [H], alpha [1]) with an out")
+        a.norm = NORM_DYNAMIC_TANH
+        a.weight, a.bias, a.alpha = (_dev(w, "weight", torch.float32), _dev(b, "bias", torch.float32),
+                                     _dev(alpha, "alpha", torch.float32))
+    if out is not None and out.numel() != n_rows * H:
+        raise KernelError("stream_add_norm: out has the wrong size")
+    a.out = _dev(out, "out")
+    a.dtype = _code(dense[0], "stream_add_norm") if dense else F32
+    a.rows = _dev(rows, "rows", torch.int32)
+    a.n_rows, a.hidden = n_rows, H
+    _check(_lib().ftk_stream_add_norm(ctypes.byref(a), _stream()), "stream_add_norm")
+
+
+def head_gate(o: torch.Tensor, gates: torch.Tensor) -> None:
+    """``o[t, h, :] *= sigmoid(gates[t, h])`` in place; ``gates`` may be a view of columns of a wider
+    row-major tensor (its row stride is taken, its columns must be adjacent)."""
+    T, Hq, D = o.shape
+    if gates.shape != (T, Hq) or gates.dtype != o.dtype or gates.stride(1) != 1 or not gates.is_cuda:
+        raise KernelError("head_gate: gates must be [T, heads] of o's dtype with adjacent columns")
+    _check(_lib().ftk_head_gate(_dev(o, "o"), _code(o, "o"), gates.data_ptr(), gates.stride(0) if T > 1 else Hq, T, Hq, D,
+                                _stream()), "head_gate")
+
+
+def table_route(token_ids: torch.Tensor, table: torch.Tensor, n_experts: int, ids: torch.Tensor,
+                weights: torch.Tensor) -> None:
+    """``ids[t, j] = table[token_ids[t], j]``, ``weights[t, j] = 1 / top``: experts by a table over token ids."""
+    V, k = table.shape
+    T = ids.shape[0]
+    if ids.shape != (T, k) or weights.shape != (T, k) or token_ids.numel() < T:
+        raise KernelError("table_route: ids / weights must be [T, top]")
+    _check(_lib().ftk_table_route(_dev(token_ids, "token_ids", torch.int32), _dev(table, "table", torch.int32), T, V, k,
+                                  int(n_experts), 1.0 / k, _dev(ids, "ids", torch.int32),
+                                  _dev(weights, "weights", torch.float32), _stream()), "table_route")
+
+
+def scale_(x: torch.Tensor, s: float) -> None:
+    """``x *= s`` for a float32 tensor."""
+    _check(_lib().ftk_scale_f32(_dev(x, "x", torch.float32), x.numel(), float(s), _stream()), "scale")

@@ -23,7 +23,7 @@ import torch
 from ..config.spec import ModelSpec, ParamSpec, PartSpec
 from ..errors import ConfigError
 from ..parts import BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, BuildEnv, Part, StepState
-from ..parts.base import as_rows, nvtx_range
+from ..parts.base import StreamSum, as_rows, nvtx_range
 
 
 def _walk(prefix: str, part: Part, out: Dict[str, Tuple[Part, str, ParamSpec]]) -> None:
@@ -51,12 +51,18 @@ class Model:
             self.blocks.append(BLOCKS.build(ls.block, env, mixer=mixer, ffn=ffn,
                                             mixer_name=ls.mixer_name, ffn_name=ls.ffn_name))
         self.final_norm = NORMS.build(spec.final_norm, env)
+        self.pass_vectors = None
+        if spec.pass_vectors is not None:
+            self.pass_vectors = EMBEDDINGS.build(PartSpec(spec.pass_vectors.kind,
+                                                          {"hidden": self.hidden, **spec.pass_vectors.params}), env)
         self._index: Dict[str, Tuple[Part, str, ParamSpec]] = {}
         _walk(spec.embedding_name, self.embedding, self._index)
         _walk(spec.head_name, self.head, self._index)
         for ls, block in zip(spec.layers, self.blocks):
             _walk(ls.name, block, self._index)
         _walk(spec.final_norm_name, self.final_norm, self._index)
+        if self.pass_vectors is not None:
+            _walk(spec.pass_vectors_name, self.pass_vectors, self._index)
 
     # ------------------------------------------------------------------ tensors
     def param_specs(self) -> Dict[str, ParamSpec]:
@@ -106,8 +112,9 @@ class Model:
             for c in p.children().values():
                 visit(c)
 
-        for p in (self.embedding, *self.blocks, self.final_norm, self.head):
-            visit(p)
+        for p in (self.embedding, *self.blocks, self.final_norm, self.head, self.pass_vectors):
+            if p is not None:
+                visit(p)
         for p in self.env.shared.values():
             if isinstance(p, Part):
                 visit(p)
@@ -138,6 +145,14 @@ class Model:
         self.embedding.forward(step.token_ids, residual)
         x = None
         for i, e in enumerate(self.spec.schedule):
+            if e.add_embedding or e.add_pass_vector is not None:
+                # fed into the stream with whatever the layer before left to be added: the entry's first norm
+                # (or, for a norm that cannot, one launch of its own) takes all of it in one 32-bit sum
+                x = StreamSum.of(x) if x is not None else StreamSum()
+                if e.add_embedding:
+                    x.add_rows_of(self.embedding.table(), step.token_ids)
+                if e.add_pass_vector is not None:
+                    x.add_vector(self.pass_vectors.vector(e.add_pass_vector))
             with nvtx_range(f"layer {e.layer}"):
                 x = self.blocks[e.layer].forward(x, residual, step, cache_views[i], e.cache_from is None)
         R = step.n_logit_rows
@@ -150,6 +165,6 @@ class Model:
             logits = ws.get("model.logits", (R, self.vocab), torch.float32)
         y = ws.get("model.final", (R, self.hidden), dt, (cap, self.hidden))
         with nvtx_range("final norm + head"):
-            self.final_norm.add_forward(as_rows(x, self.final_norm), residual, y, rows=step.logit_rows)
+            self.final_norm.add_forward(as_rows(x, self.final_norm, residual), residual, y, rows=step.logit_rows)
             self.head.forward(y, logits)
         return logits

@@ -188,9 +188,94 @@ class RouteSum:
         return self.out
 
 
-def as_rows(x: Any, consumer: Any = None) -> Any:
+class StreamSum:
+    """Rows still to be added to the 32-bit stream, each kind at most as often as the kernel that adds
+    them takes it: up to two dense ``[T, hidden]`` tensors, one :class:`RouteSum`, the rows of a table
+    picked by token id (``table [vocab, hidden]``, ``ids [T]``) and one ``[hidden]`` vector for every
+    token.  A layer with two sub-layers on one norm hands both outputs on this way, and a model adds
+    what it feeds into the stream between layers (its input embedding once more, a vector per pass).
+    A norm with ``takes_stream_sum`` adds everything in the pass that norms; for any other consumer
+    :meth:`fold` adds it to the stream first."""
+
+    def __init__(self) -> None:
+        self.dense: List[torch.Tensor] = []
+        self.routes: Optional[RouteSum] = None
+        self.table: Optional[torch.Tensor] = None
+        self.ids: Optional[torch.Tensor] = None
+        self.vec: Optional[torch.Tensor] = None
+
+    @staticmethod
+    def of(x: Any) -> "StreamSum":
+        if isinstance(x, StreamSum):
+            return x
+        out = StreamSum()
+        out.add(x)
+        return out
+
+    def add(self, x: Any) -> "StreamSum":
+        if x is None:
+            return self
+        if isinstance(x, RouteSum):
+            if self.routes is not None:
+                self.dense.append(self.routes.rows())
+            self.routes = x
+        elif isinstance(x, StreamSum):
+            for d in x.dense:
+                self.add(d)
+            self.add(x.routes)
+            if x.table is not None:
+                self.add_rows_of(x.table, x.ids)
+            if x.vec is not None:
+                self.add_vector(x.vec)
+        else:
+            self.dense.append(x)
+        return self
+
+    def add_rows_of(self, table: torch.Tensor, ids: torch.Tensor) -> "StreamSum":
+        if self.table is not None:
+            raise ConfigError("StreamSum: rows of one table only")
+        self.table, self.ids = table, ids
+        return self
+
+    def add_vector(self, vec: torch.Tensor) -> "StreamSum":
+        if self.vec is not None:
+            raise ConfigError("StreamSum: one vector only")
+        self.vec = vec
+        return self
+
+    def kernel_args(self, residual: torch.Tensor) -> Dict[str, Any]:
+        """Keyword arguments of ``ops.stream_add_norm``; addends beyond what one launch takes (a third
+        dense tensor, routed rows with a shared part) are added to ``residual`` by launches of their own."""
+        from ..kernels import ops
+
+        dense = list(self.dense)
+        routed = None
+        if self.routes is not None:
+            r = self.routes
+            routed = (r.y, r.pos, r.top_k)
+            if r.shared is not None:
+                dense.append(r.shared)
+        while len(dense) > 2:
+            ops.stream_add_norm(residual, None, x1=dense.pop())
+        return dict(x1=dense[0] if dense else None, x2=dense[1] if len(dense) > 1 else None, routed=routed,
+                    table=self.table, ids=self.ids, vec=self.vec)
+
+    def fold(self, residual: torch.Tensor) -> None:
+        """Add everything to ``residual`` now."""
+        from ..kernels import ops
+
+        ops.stream_add_norm(residual, None, **self.kernel_args(residual))
+
+
+def as_rows(x: Any, consumer: Any = None, residual: Optional[torch.Tensor] = None) -> Any:
     """``x`` as the consumer can take it: a :class:`RouteSum` stays one only for a norm that says it
-    takes one."""
+    takes one; a :class:`StreamSum` stays one only for a norm with ``takes_stream_sum`` and is otherwise
+    added to ``residual`` at once (nothing is then left to hand on)."""
+    if isinstance(x, StreamSum) and not getattr(consumer, "takes_stream_sum", False):
+        if residual is None:
+            raise ConfigError("a StreamSum needs the stream to be added to")
+        x.fold(residual)
+        return None
     if isinstance(x, RouteSum) and not getattr(consumer, "takes_route_sum", False):
         return x.rows()
     return x
@@ -198,6 +283,7 @@ def as_rows(x: Any, consumer: Any = None) -> Any:
 
 class Norm(Part):
     takes_route_sum: bool = False  # add_forward accepts a RouteSum as x
+    takes_stream_sum: bool = False  # add_forward accepts a StreamSum as x
 
     def forward(self, x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         """``out = norm(x)`` row by row."""

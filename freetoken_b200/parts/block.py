@@ -1,9 +1,14 @@
-"""Arrangement of the parts in one layer.
+"""Arrangements of the parts in one layer.
 
 ``prenorm_residual`` (python/freetoken/models/minimax_m3/model.py:53-61): every norm call is
 "add the previous sub-layer's output to the residual, then norm the sum":
 ``r += x; h = N_in(r); a = mixer(h); r += a; h = N_post(r); f = ffn(h)`` and ``f`` travels to
 the next layer's first norm.  The residual stream is 32-bit.
+
+``parallel_residual``: one norm feeds both sub-layers, ``r += x; h = N(r); a = mixer(h); f = ffn(h)``,
+and ``a + f`` travels to the next layer's norm as a :class:`StreamSum`, so that both are added to
+the 32-bit stream in 32 bits, by the kernel that norms.  A layer without feed-forward names the
+feed-forward kind ``none``.
 """
 
 from __future__ import annotations
@@ -13,7 +18,8 @@ from typing import Any, Dict, Optional
 import torch
 
 from ..config.spec import PartSpec
-from .base import BLOCKS, NORMS, Block, BuildEnv, FeedForward, Mixer, Part, StepState, as_rows, nvtx_range
+from .base import (BLOCKS, FEED_FORWARDS, NORMS, Block, BuildEnv, FeedForward, Mixer, Part, StepState, StreamSum, as_rows,
+                   nvtx_range)
 
 
 @BLOCKS.register("prenorm_residual")
@@ -43,7 +49,7 @@ class PreNormResidualBlock(Block):
         T = residual.shape[0]
         ws, dt, cap = self.env.workspace, self.env.dtype, self.env.max_step_tokens
         h = ws.get("block.h", (T, self.hidden), dt, (cap, self.hidden))
-        self.input_norm.add_forward(as_rows(x, self.input_norm), residual, h)
+        self.input_norm.add_forward(as_rows(x, self.input_norm, residual), residual, h)
         with nvtx_range(f"mixer {self.mixer.kind}"):
             a = self.mixer.forward(h, step, cache, writes_cache)
         h2 = ws.get("block.h2", (T, self.hidden), dt, (cap, self.hidden))
@@ -54,3 +60,47 @@ class PreNormResidualBlock(Block):
         lazy = getattr(self.ffn, "forward_lazy", None)
         with nvtx_range(f"feed-forward {self.ffn.kind}"):
             return lazy(h2, step, h_f32=h32) if lazy is not None else self.ffn.forward(h2, step, h_f32=h32)
+
+
+@FEED_FORWARDS.register("none")
+class NoFeedForward(FeedForward):
+    """A layer without feed-forward: owns nothing, adds nothing."""
+
+    def forward(self, h: torch.Tensor, step: StepState, h_f32: Optional[torch.Tensor] = None):
+        return None
+
+
+@BLOCKS.register("parallel_residual")
+class ParallelResidualBlock(Block):
+    """params: ``hidden``, ``norm`` (PartSpec of the layer's one norm), ``norm_name`` (weight-name part)."""
+
+    def __init__(self, spec: PartSpec, env: BuildEnv, mixer: Mixer, ffn: FeedForward,
+                 mixer_name: str, ffn_name: str):
+        super().__init__(spec, env, mixer, ffn, mixer_name, ffn_name)
+        self.hidden = int(spec["hidden"])
+        self.norm = NORMS.build(spec["norm"], env)
+        self.norm_name = spec.get("norm_name", "input_layernorm")
+        self.has_ffn = not isinstance(ffn, NoFeedForward)
+
+    def children(self) -> Dict[str, Part]:
+        out = {self.norm_name: self.norm, self.mixer_name: self.mixer}
+        if self.has_ffn:
+            out[self.ffn_name] = self.ffn
+        return out
+
+    def workspace_bytes(self, n_tokens: int) -> int:
+        item = 4 if self.env.dtype == torch.float32 else 2
+        return n_tokens * self.hidden * item
+
+    def forward(self, x, residual: torch.Tensor, step: StepState, cache: Any, writes_cache: bool):
+        T = residual.shape[0]
+        ws, dt, cap = self.env.workspace, self.env.dtype, self.env.max_step_tokens
+        h = ws.get("block.h", (T, self.hidden), dt, (cap, self.hidden))
+        self.norm.add_forward(as_rows(x, self.norm, residual), residual, h)
+        with nvtx_range(f"mixer {self.mixer.kind}"):
+            out = StreamSum().add(self.mixer.forward(h, step, cache, writes_cache))
+        if self.has_ffn:
+            lazy = getattr(self.ffn, "forward_lazy", None)
+            with nvtx_range(f"feed-forward {self.ffn.kind}"):
+                out.add(lazy(h, step, h_f32=None) if lazy is not None else self.ffn.forward(h, step))
+        return out

@@ -48,13 +48,14 @@ class TokenEmbedding(Embedding):
 
 @HEADS.register("linear_head")
 class LinearHead(Head):
-    """params: ``vocab``, ``hidden``, ``tied`` (bool: multiply by the embedding's table)."""
+    """params: ``vocab``, ``hidden``, ``tied`` (bool: multiply by the embedding's table), ``scale`` (1.0)."""
 
     def __init__(self, spec: PartSpec, env: BuildEnv):
         super().__init__(spec, env)
         self.vocab = int(spec["vocab"])
         self.hidden = int(spec["hidden"])
         self.tied = bool(spec.get("tied", False))
+        self.scale = float(spec.get("scale", 1.0))  # logits are multiplied by it
         self._tied_weight: Optional[torch.Tensor] = None
 
     def param_specs(self) -> Dict[str, ParamSpec]:
@@ -75,3 +76,27 @@ class LinearHead(Head):
             torch.matmul(y, w.t(), out=logits)
         else:
             torch.mm(y, w.t(), out=logits, out_dtype=torch.float32)
+        if self.scale != 1.0:
+            ops.scale_(logits, self.scale)
+
+
+@EMBEDDINGS.register("pass_vectors")
+class PassVectors(Embedding):
+    """One ``[hidden]`` vector per pass of a repeated range of layers, added to every token of the
+    stream before the pass (``table [passes, hidden]``, kept in 32-bit).  It is an embedding of the pass
+    number rather than of a token; :meth:`vector` gives the row."""
+
+    def __init__(self, spec: PartSpec, env: BuildEnv):
+        super().__init__(spec, env)
+        self.passes = int(spec["passes"])
+        self.hidden = int(spec["hidden"])
+        self.local_name = spec.get("name", "weight")
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        return {self.local_name: ParamSpec((self.passes, self.hidden), "float32", ("normal", 0.0, 0.02), store="bfloat16")}
+
+    def vector(self, i: int) -> torch.Tensor:
+        return self.params[self.local_name][i]
+
+    def table(self) -> torch.Tensor:
+        return self.params[self.local_name]

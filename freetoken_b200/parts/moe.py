@@ -12,6 +12,10 @@ product with ``gate_up_proj [E, 2I, H]``, activation on the two halves, grouped 
 (python/freetoken/kernel/triton/fused_moe.py:292-296), then the sum over a token's routes in
 route order with a 32-bit accumulator (:111-153).  The shared expert runs on the same input
 and is added (moe.py:87-88).
+
+``router="token_table"`` has no router matrix: a table ``[vocab, top_k]`` of expert ids (the ids of a
+row differ) names each token id's experts, each with weight ``1 / top_k``; the expert products are
+the same kernels.  The reference has no such router.
 """
 
 from __future__ import annotations
@@ -55,7 +59,8 @@ def split_in_three(w: torch.Tensor) -> Optional[torch.Tensor]:
 class MoE(FeedForward):
     """params: ``hidden``, ``inter``, ``n_experts``, ``top_k``, ``scoring`` ("sigmoid" |
     "softmax"), ``bias`` (bool), ``scale``, ``act``, ``alpha``, ``limit``,
-    ``shared_inter`` (0 = no shared expert).  ``h_f32`` given to the forward calls of a bfloat16 model
+    ``shared_inter`` (0 = no shared expert), ``router`` ("learned" | "token_table"; the table also needs
+    ``vocab``).  ``h_f32`` given to the forward calls of a bfloat16 model
     is ``float32(h)``, as a norm's ``out_f32`` is."""
 
     wants_f32_input = True
@@ -77,6 +82,13 @@ class MoE(FeedForward):
         self.alpha = float(spec.get("alpha", 1.702))
         self.limit = float(spec.get("limit", 7.0))
         self.shared_inter = int(spec.get("shared_inter", 0) or 0)
+        self.router = spec.get("router", "learned")
+        if self.router not in ("learned", "token_table"):
+            raise ConfigError(f"moe: unknown router '{self.router}'")
+        self.by_table = self.router == "token_table"
+        self.vocab = int(spec.get("vocab", 0) or 0)
+        if self.by_table and self.vocab < 1:
+            raise ConfigError("moe: a token-table router needs the vocabulary size")
         self._gate_pieces: Optional[torch.Tensor] = None
         self.shared: Optional[GatedMLP] = None
         if self.shared_inter:
@@ -86,10 +98,13 @@ class MoE(FeedForward):
 
     def param_specs(self) -> Dict[str, ParamSpec]:
         out = {
-            "gate.weight": ParamSpec((self.n_experts, self.hidden), "float32"),
             "experts.gate_up_proj": ParamSpec((self.n_experts, 2 * self.inter, self.hidden)),
             "experts.down_proj": ParamSpec((self.n_experts, self.hidden, self.inter)),
         }
+        if self.by_table:
+            out["table"] = ParamSpec((self.vocab, self.top_k), "int32", ("distinct_ids", self.n_experts))
+        else:
+            out["gate.weight"] = ParamSpec((self.n_experts, self.hidden), "float32")
         if self.has_bias:
             out["e_score_correction_bias"] = ParamSpec((self.n_experts,), "float32", ("normal", 0.0, 0.01))
         return out
@@ -98,6 +113,8 @@ class MoE(FeedForward):
         return {"shared_experts": self.shared} if self.shared is not None else {}
 
     def f32_input_needed(self, n_tokens: int) -> bool:
+        if self.by_table:
+            return False
         # long bfloat16 steps take the router product from the bfloat16 rows themselves
         return not (self._gate_pieces is not None and self.env.dtype == torch.bfloat16
                     and not ops.moe_route_fits(n_tokens, self.hidden, self.n_experts, self.top_k))
@@ -105,7 +122,7 @@ class MoE(FeedForward):
     def bind(self, tensors) -> None:
         super().bind(tensors)
         self._gate_pieces = None
-        if self.env.dtype == torch.bfloat16 and SPLIT_ROUTER_PRODUCT:
+        if self.env.dtype == torch.bfloat16 and SPLIT_ROUTER_PRODUCT and not self.by_table:
             self._gate_pieces = split_in_three(self.params["gate.weight"])
 
     def workspace_bytes(self, n_tokens: int) -> int:
@@ -123,7 +140,10 @@ class MoE(FeedForward):
         T = h.shape[0]
         ws, dt, cap = self.env.workspace, self.env.dtype, self.env.max_step_tokens
         k, R = self.top_k, T * self.top_k
-        ops.moe_route(h_f32, self.params["gate.weight"], bias, k, self.scoring, self.scale, logits, ids, wts)
+        if self.by_table:
+            ops.table_route(step.token_ids, self.params["table"], self.n_experts, ids, wts)
+        else:
+            ops.moe_route(h_f32, self.params["gate.weight"], bias, k, self.scoring, self.scale, logits, ids, wts)
         record = self.env.shared.get("record_expert_counts")
         if record is not None:
             record.append(torch.bincount(ids.view(-1).long(), minlength=self.n_experts).to(torch.int32))
@@ -144,7 +164,9 @@ class MoE(FeedForward):
         T = h.shape[0]
         ws, dt, cap = self.env.workspace, self.env.dtype, self.env.max_step_tokens
         k, E, R = self.top_k, self.n_experts, T * self.top_k
-        if h_f32 is None and self.f32_input_needed(T):
+        if self.by_table:
+            h_f32 = None
+        elif h_f32 is None and self.f32_input_needed(T):
             if h.dtype == torch.float32:
                 h_f32 = h
             else:
@@ -159,9 +181,12 @@ class MoE(FeedForward):
         pos = ws.get("moe.pos", (R,), torch.int32, (cap * k,))
         bias = self.params.get("e_score_correction_bias")
         if (dt == torch.bfloat16 and ops.moe_small_fits(T, self.hidden, self.inter, k)
-                and ops.moe_route_fits(T, self.hidden, E, k)):
+                and (self.by_table or ops.moe_route_fits(T, self.hidden, E, k))):
             return self._few_tokens(h, h_f32, step, logits, ids, wts, bias)
-        if ops.moe_route_fits(T, self.hidden, E, k):  # small steps: logits, choice and sort in one launch
+        if self.by_table:  # the table names the experts; the sort is the one every router's choice gets
+            ops.table_route(step.token_ids, self.params["table"], E, ids, wts)
+            ops.moe_permute(ids, E, counts, offsets, routes, pos)
+        elif ops.moe_route_fits(T, self.hidden, E, k):  # small steps: logits, choice and sort in one launch
             ops.moe_route(h_f32, self.params["gate.weight"], bias, k, self.scoring, self.scale, logits, ids, wts,
                           counts, offsets, routes, pos)
         elif self._gate_pieces is not None and h.dtype == torch.bfloat16:

@@ -10,6 +10,11 @@ their own kernels (``norm_rope_store``); one table serves all layers with equal 
 (``get_rope`` is cached the same way, rotary.py:211-231).
 
 ``none``: no position encoding (a mixer that needs none asks for this kind).
+
+``log_temperature``: no rotation; the table holds one factor per position,
+``1 + coef * ln(floor((p + 1) / every) + 1)``, by which a mixer multiplies its queries, so that
+attention sharpens as the context grows.  Computed in float64 on the host and rounded once to
+float32.
 """
 
 from __future__ import annotations
@@ -45,6 +50,32 @@ class NeoxRope(PositionEncoding):
             t = torch.arange(self.env.max_seq_len, dtype=torch.float)
             freqs = torch.einsum("i,j -> ij", t, inv_freq)
             self._table = torch.cat((freqs.cos(), freqs.sin()), dim=-1).contiguous().to(self.env.device)
+        return self._table
+
+
+@POSITIONS.register("log_temperature")
+class LogTemperature(PositionEncoding):
+    """params: ``coef``, ``every`` (positive integer)."""
+
+    rotary_dim = 0
+
+    def __init__(self, spec: PartSpec, env: BuildEnv):
+        super().__init__(spec, env)
+        self.coef = float(spec["coef"])
+        self.every = int(spec["every"])
+        if self.every < 1:
+            raise ConfigError(f"log_temperature: every={self.every} must be >= 1")
+        self._table: Optional[torch.Tensor] = None
+
+    def table(self) -> Optional[torch.Tensor]:
+        return None  # nothing to rotate by
+
+    def scale_table(self) -> torch.Tensor:
+        """``[positions]`` float32 factors, built at the first call (see :meth:`NeoxRope.table`)."""
+        if self._table is None:
+            p = torch.arange(self.env.max_seq_len, dtype=torch.int64)
+            steps = torch.div(p + 1, self.every, rounding_mode="floor") + 1
+            self._table = (1.0 + self.coef * torch.log(steps.double())).float().contiguous().to(self.env.device)
         return self._table
 
 

@@ -1,4 +1,5 @@
-"""One registry from an architecture's name (``config.json``'s ``architectures[0]``) to its model.
+"""One registry from an architecture's name (``config.json``'s ``architectures[0]``, or its
+``architecture`` string) to its model.
 
 An :class:`Architecture` bundles what is specific to one model family: how to read its
 config.json into a typed config, how to turn that into a :class:`ModelSpec`, and how its
@@ -27,12 +28,15 @@ class Architecture:
     fusion_rules: Callable[[Any], List[Any]] = lambda cfg: []
     name_prefixes: Tuple[str, ...] = ()  # prefixes dropped from checkpoint tensor names
     ignorable: Callable[[str], bool] = lambda name: False  # checkpoint tensors never read
+    # sizes that only the weight file states: (typed config, {checkpoint tensor name: shape}) -> typed config
+    sizes_from_weights: Optional[Callable[[Any, Mapping[str, Tuple[int, ...]]], Any]] = None
 
 
 _REGISTRY: Dict[str, Architecture] = {}
 _LAZY: Dict[str, str] = {
     "MiniMaxM3SparseForCausalLM": "freetoken_b200.models.minimax_m3",
     "MiniMaxM3SparseForConditionalGeneration": "freetoken_b200.models.minimax_m3",
+    "Rumalorn": "freetoken_b200.models.rumalorn",
 }
 
 
@@ -56,8 +60,10 @@ def get_architecture(name: str) -> Architecture:
 
 def architecture_of(raw: Mapping[str, Any]) -> Architecture:
     archs = raw.get("architectures")
+    if not archs and isinstance(raw.get("architecture"), str):  # some files name their one architecture as a string
+        archs = [raw["architecture"]]
     if not archs:
-        raise ConfigError("config.json: 'architectures' is missing or empty")
+        raise ConfigError("config.json: 'architectures' (or 'architecture') is missing or empty")
     return get_architecture(str(archs[0]))
 
 

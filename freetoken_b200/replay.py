@@ -51,6 +51,7 @@ def main(argv: Optional[List[str]] = None) -> int:
 
     from .config.engine_config import EngineConfig
     from .config.reader import read_config_json
+    from .engine.build import typed_config
     from .engine.engine import Engine, StepEntry
     from .errors import FreeTokenError
     from .registry import architecture_of
@@ -60,7 +61,7 @@ def main(argv: Optional[List[str]] = None) -> int:
     try:
         raw = read_config_json(args.model)
         arch = architecture_of(raw)  # the architecture says how long its sequences may get
-        seq = min(int(arch.build_spec(arch.parse_config(raw)).max_position), n_pages * page)
+        seq = min(int(arch.build_spec(typed_config(arch, raw, args.model)).max_position), n_pages * page)
         engine = Engine(EngineConfig(
             model_path=args.model, dtype=args.dtype, device=args.device, page_size=page, num_page_override=n_pages,
             max_running_req=MAX_LIVE, max_seq_len_override=seq, max_extend_tokens=seq,

@@ -11,7 +11,7 @@ values do not depend on creation order.
 
 Distributions come from each parameter's ``init``: weights ``N(0, 0.02)``, norm scales
 ``N(0, 0.02)`` in the Gemma (1+w) form or ``1 + N(0, 0.02)`` otherwise, router bias
-``N(0, 0.01)``.
+``N(0, 0.01)``; ``("distinct_ids", n)`` fills an integer table with rows of different ids below ``n``.
 """
 
 from __future__ import annotations
@@ -48,6 +48,11 @@ def _draw(ps: ParamSpec, gen: torch.Generator, device, dtype: torch.dtype) -> to
         t = torch.empty(ps.shape, dtype=torch.float32 if dtype != torch.bfloat16 else dtype, device=device)
         t.normal_(mean, std, generator=gen)
         return t.to(dtype)
+    if kind == "distinct_ids":  # rows of different ids below ps.init[1] (a table that names experts)
+        n = int(ps.init[1])
+        rows, k = ps.shape
+        keys = torch.rand((rows, n), generator=gen, device=device)
+        return keys.argsort(dim=1)[:, :k].to(dtype).contiguous()
     raise ValueError(f"unknown init {ps.init!r}")
 
 

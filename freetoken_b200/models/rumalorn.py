@@ -51,29 +51,33 @@ def build_spec(cfg: RumalornConfig) -> ModelSpec:
     norm = PartSpec("dynamic_tanh", dict(size=cfg.width))
     block = PartSpec("parallel_residual", dict(hidden=cfg.width, norm=norm, norm_name="norm1"))
     layers: List[LayerSpec] = []
+    # random models: spreads that keep every activation of order one, so that a fault anywhere shows in the logits
+    w_in = cfg.width ** -0.5
     for i, l in enumerate(cfg.layers):
         a = l.mixer
         buckets = cfg.rel_buckets[i] if i < len(cfg.rel_buckets) and cfg.rel_buckets[i] else DEFAULT_BUCKETS
         mixer = PartSpec("tied_kv_attention", dict(
             hidden=cfg.width, n_heads=a.heads, n_kv_heads=a.kv_heads, head_dim=a.dim, scale=a.scale,
             proj_bias=True, gate=True, buckets=buckets, max_distance=a.bias_max,
-            position=PartSpec("log_temperature", dict(coef=a.q_temp_coef, every=a.q_temp_every)), window=None))
+            position=PartSpec("log_temperature", dict(coef=a.q_temp_coef, every=a.q_temp_every)), window=None,
+            init_std=(w_in, 0.5 * (a.heads * a.dim) ** -0.5)))
         if l.mlp is None:
             ffn = PartSpec("none")
         elif l.mlp.kind == "dense":
             ffn = PartSpec("gated_mlp", dict(hidden=cfg.width, inter=l.mlp.ff, act="swigluoai", alpha=1.702,
-                                             limit=l.mlp.limit))
+                                             limit=l.mlp.limit, init_std=(w_in, 0.5 * l.mlp.ff ** -0.5)))
         else:
             ffn = PartSpec("moe", dict(hidden=cfg.width, inter=l.mlp.ff, n_experts=l.mlp.experts, top_k=l.mlp.top,
-                                       router="token_table", vocab=cfg.vocab, act="silu", scale=1.0))
+                                       router="token_table", vocab=cfg.vocab, act="silu", scale=1.0,
+                                       init_std=(w_in, 0.5 * l.mlp.ff ** -0.5)))
         layers.append(LayerSpec(name=f"l{i}", block=block, mixer=mixer, ffn=ffn, mixer_name="mix", ffn_name="mlp"))
     schedule = tuple(ScheduleEntry(l, None, emb, vec) for l, emb, vec in layer_passes(cfg))
     return ModelSpec(
         architecture=cfg.architecture, vocab_size=cfg.vocab, hidden_size=cfg.width, layers=tuple(layers),
         schedule=schedule,
-        embedding=PartSpec("token_embedding", dict(vocab=cfg.vocab, hidden=cfg.width)),
+        embedding=PartSpec("token_embedding", dict(vocab=cfg.vocab, hidden=cfg.width, init_std=1.0)),
         final_norm=norm,
-        head=PartSpec("linear_head", dict(tied=False, scale=cfg.logit_scale)),
+        head=PartSpec("linear_head", dict(tied=False, scale=cfg.logit_scale, init_std=w_in)),
         max_position=MAX_POSITION,
         embedding_name="embed_tokens", final_norm_name="final.norm", head_name="head",
         pass_vectors=PartSpec("pass_vectors", dict(passes=cfg.loop_times, name="step")) if cfg.loop_times else None,

@@ -29,15 +29,16 @@ from .base import EMBEDDINGS, HEADS, BuildEnv, Embedding, Head
 
 @EMBEDDINGS.register("token_embedding")
 class TokenEmbedding(Embedding):
-    """params: ``vocab``, ``hidden``."""
+    """params: ``vocab``, ``hidden``, ``init_std`` (spread of random weights, 0.02)."""
 
     def __init__(self, spec: PartSpec, env: BuildEnv):
         super().__init__(spec, env)
         self.vocab = int(spec["vocab"])
         self.hidden = int(spec["hidden"])
+        self.init_std = float(spec.get("init_std", 0.02))
 
     def param_specs(self) -> Dict[str, ParamSpec]:
-        return {"weight": ParamSpec((self.vocab, self.hidden))}
+        return {"weight": ParamSpec((self.vocab, self.hidden), init=("normal", 0.0, self.init_std))}
 
     def forward(self, token_ids: torch.Tensor, residual: torch.Tensor) -> None:
         ops.embedding_gather(self.params["weight"], token_ids, residual)
@@ -59,7 +60,8 @@ class LinearHead(Head):
         self._tied_weight: Optional[torch.Tensor] = None
 
     def param_specs(self) -> Dict[str, ParamSpec]:
-        return {} if self.tied else {"weight": ParamSpec((self.vocab, self.hidden))}
+        init = ("normal", 0.0, float(self.spec.get("init_std", 0.02)))
+        return {} if self.tied else {"weight": ParamSpec((self.vocab, self.hidden), init=init)}
 
     def tie(self, embedding: Embedding) -> None:
         w = embedding.table()
@@ -93,7 +95,7 @@ class PassVectors(Embedding):
         self.local_name = spec.get("name", "weight")
 
     def param_specs(self) -> Dict[str, ParamSpec]:
-        return {self.local_name: ParamSpec((self.passes, self.hidden), "float32", ("normal", 0.0, 0.02), store="bfloat16")}
+        return {self.local_name: ParamSpec((self.passes, self.hidden), "float32", ("normal", 0.0, 0.3), store="bfloat16")}
 
     def vector(self, i: int) -> torch.Tensor:
         return self.params[self.local_name][i]

@@ -22,7 +22,7 @@ from .base import FEED_FORWARDS, BuildEnv, FeedForward, StepState
 
 @FEED_FORWARDS.register("gated_mlp")
 class GatedMLP(FeedForward):
-    """params: ``hidden``, ``inter``, ``act`` ("silu" | "swigluoai"), ``alpha``, ``limit``."""
+    """params: ``hidden``, ``inter``, ``act`` ("silu" | "swigluoai"), ``alpha``, ``limit``, ``init_std``."""
 
     def __init__(self, spec: PartSpec, env: BuildEnv, tag: str = "mlp"):
         super().__init__(spec, env)
@@ -36,9 +36,11 @@ class GatedMLP(FeedForward):
         self.tag = tag
 
     def param_specs(self) -> Dict[str, ParamSpec]:
+        std = self.spec.get("init_std")  # spread of random weights: (into the layer, out of it), default 0.02
+        std_in, std_out = (float(std[0]), float(std[1])) if std else (0.02, 0.02)
         return {
-            "gate_up_proj.weight": ParamSpec((2 * self.inter, self.hidden)),
-            "down_proj.weight": ParamSpec((self.hidden, self.inter)),
+            "gate_up_proj.weight": ParamSpec((2 * self.inter, self.hidden), init=("normal", 0.0, std_in)),
+            "down_proj.weight": ParamSpec((self.hidden, self.inter), init=("normal", 0.0, std_out)),
         }
 
     def workspace_bytes(self, n_tokens: int) -> int:

@@ -97,9 +97,11 @@ class MoE(FeedForward):
                 limit=self.limit)), env, tag="moe.shared")
 
     def param_specs(self) -> Dict[str, ParamSpec]:
+        std = self.spec.get("init_std")  # spread of random expert weights: (into the expert, out of it), default 0.02
+        std_in, std_out = (float(std[0]), float(std[1])) if std else (0.02, 0.02)
         out = {
-            "experts.gate_up_proj": ParamSpec((self.n_experts, 2 * self.inter, self.hidden)),
-            "experts.down_proj": ParamSpec((self.n_experts, self.hidden, self.inter)),
+            "experts.gate_up_proj": ParamSpec((self.n_experts, 2 * self.inter, self.hidden), init=("normal", 0.0, std_in)),
+            "experts.down_proj": ParamSpec((self.n_experts, self.hidden, self.inter), init=("normal", 0.0, std_out)),
         }
         if self.by_table:
             out["table"] = ParamSpec((self.vocab, self.top_k), "int32", ("distinct_ids", self.n_experts))

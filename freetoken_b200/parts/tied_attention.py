@@ -64,7 +64,7 @@ class TiedKVAttention(Mixer):
     """params: ``hidden``, ``n_heads``, ``n_kv_heads``, ``head_dim``, ``scale`` (None = head_dim^-0.5),
     ``proj_bias`` (bool: q, k and output projection have biases), ``gate`` (bool), ``buckets`` and
     ``max_distance`` (0 buckets = no distance bias), ``position`` (PartSpec with a ``scale_table``, or
-    None), ``window`` (None or tokens)."""
+    None), ``window`` (None or tokens), ``init_std``."""
 
     graph_safe = True  # running a step twice writes the same keys again
 
@@ -102,14 +102,16 @@ class TiedKVAttention(Mixer):
 
     # ------------------------------------------------------------------ tensors
     def param_specs(self) -> Dict[str, ParamSpec]:
+        std = self.spec.get("init_std")  # spread of random weights: (projections of the input, output projection)
+        std_in, std_out = (float(std[0]), float(std[1])) if std else (0.02, 0.02)
         out = {
-            "qkg_proj.weight": ParamSpec((self.proj_rows, self.hidden)),
-            "o_proj.weight": ParamSpec((self.hidden, self.q_dim)),
+            "qkg_proj.weight": ParamSpec((self.proj_rows, self.hidden), init=("normal", 0.0, std_in)),
+            "o_proj.weight": ParamSpec((self.hidden, self.q_dim), init=("normal", 0.0, std_out)),
         }
         if self.proj_bias:
-            out["q_bias"] = ParamSpec((self.q_dim,), "float32", ("normal", 0.0, 0.02), store="bfloat16")
-            out["k_bias"] = ParamSpec((self.kv_dim,), "float32", ("normal", 0.0, 0.02), store="bfloat16")
-            out["o_proj.bias"] = ParamSpec((self.hidden,), "compute", ("normal", 0.0, 0.02))
+            out["q_bias"] = ParamSpec((self.q_dim,), "float32", ("normal", 0.0, 0.3), store="bfloat16")
+            out["k_bias"] = ParamSpec((self.kv_dim,), "float32", ("normal", 0.0, 0.3), store="bfloat16")
+            out["o_proj.bias"] = ParamSpec((self.hidden,), "compute", ("normal", 0.0, 0.1))
         if self.buckets:
             out["rel"] = ParamSpec((self.buckets, self.n_heads), "float32", ("normal", 0.0, 0.5), store="bfloat16")
         return out

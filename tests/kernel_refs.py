@@ -77,13 +77,16 @@ def table_update(table, updates, n_updates):
 
 def norm_rope_store(x, head_dim, rotary_dim, positions, rope_table, eps, gemma, sections):
     T = x.shape[0]
-    xs = x.view(T, -1, head_dim).float()
+    whole = x.shape[1] // head_dim * head_dim  # a row may end in columns that belong to no head
+    xs = x[:, :whole].reshape(T, -1, head_dim).float()
     half = rotary_dim // 2
     if rotary_dim:
         cs = rope_table[positions.long()]
         cos, sin = cs[:, None, :half], cs[:, None, half:]
     for s in sections:
         u = xs[:, s["first_head"]: s["first_head"] + s["n_heads"]]
+        if s.get("bias") is not None:
+            u = u + s["bias"].float().view(1, s["n_heads"], head_dim)
         w = s.get("norm_weight")
         if w is not None:
             scale = w.float() + 1.0 if gemma else w.float()
@@ -91,8 +94,14 @@ def norm_rope_store(x, head_dim, rotary_dim, positions, rope_table, eps, gemma, 
         if s.get("rotate") and rotary_dim:
             a, b, rest = u[..., :half], u[..., half:rotary_dim], u[..., rotary_dim:]
             u = torch.cat([a * cos - b * sin, b * cos + a * sin, rest], dim=-1)
+        if s.get("pos_scale") is not None:
+            f = s["pos_scale"].float()
+            u = u * f[positions.long().clamp(0, f.numel() - 1)][:, None, None]
+        dst_dim = int(s.get("dst_head_dim") or head_dim)
+        if dst_dim != head_dim:
+            u = torch.cat([u, torch.zeros(*u.shape[:-1], dst_dim - head_dim, dtype=u.dtype, device=u.device)], dim=-1)
         if s.get("dense_out") is not None:
-            s["dense_out"].view(T, s["n_heads"], head_dim).copy_(u.to(x.dtype))
+            s["dense_out"].view(T, s["n_heads"], dst_dim).copy_(u.to(x.dtype))
         else:
             slab, slots = s["slab"], s["slot_map"][:T].long()
             P = slab.shape[2]
@@ -102,7 +111,7 @@ def norm_rope_store(x, head_dim, rotary_dim, positions, rope_table, eps, gemma, 
 
 
 def paged_attention(q, k_slab, v_slab, block_table, seg_info, n_segs, items, n_items, part_o, part_ml,
-                    out, tile_rows, scale, window, sel=None, block_size=0, few_rows=False):
+                    out, tile_rows, scale, window, sel=None, block_size=0, few_rows=False, dist_bias=None):
     """Per query token, softmax over the visible keys gathered through the block table; the
     work list and the scratch are ignored (they only steer how the kernel splits the work).
     With ``sel`` a query reads only the keys of its chosen blocks."""
@@ -123,6 +132,9 @@ def paged_attention(q, k_slab, v_slab, block_table, seg_info, n_segs, items, n_i
             if sel is None:
                 kk, vv = K[lo:p_q + 1], V[lo:p_q + 1]
                 s = torch.einsum("hgd,khd->hgk", qq, kk) * scale
+                if dist_bias is not None:  # [Hq, L] by distance, the last entry for everything farther
+                    dist = (p_q - torch.arange(lo, p_q + 1, device=q.device)).clamp(max=dist_bias.shape[1] - 1)
+                    s = s + dist_bias.float()[:, dist].view(Hkv, G, -1)
                 p = torch.softmax(s, dim=-1)
                 o = torch.einsum("hgk,khd->hgd", p, vv)
             else:
@@ -193,10 +205,6 @@ def moe_permute(topk_ids, n_experts, expert_counts, expert_offsets, sorted_route
     expert_offsets[1:] = torch.cumsum(counts, 0).to(torch.int32)
     sorted_routes.copy_(order.to(torch.int32))
     route_pos[order] = torch.arange(flat.numel(), dtype=torch.int32, device=flat.device)
-
-
-def linear(x, w, out):
-    out.copy_((x.float() @ w.float().T).to(out.dtype))
 
 
 def moe_gemm1_gather_fits(dtype, hidden, inter, n_experts, n_routes):
@@ -288,7 +296,63 @@ def sample(logits, temperature, top_k, top_p, u, out):
         out[r] = idx
 
 
-ALL = ["sparse_score_fits", "moe_small_fits", "copy_tokens", "sparse_select", "embedding_gather", "add_rmsnorm", "add_rmsnorm_routes", "act_and_mul", "cast", "table_update", "norm_rope_store",
+def stream_add_norm(residual, out, x1=None, x2=None, routed=None, table=None, ids=None, vec=None, norm=None, rows=None):
+    src = next(t for t in (residual, x1, x2, out) if t is not None)
+    H = src.shape[-1]
+    total = (residual if residual is not None else src).numel() // H
+    z = residual.float().view(total, H).clone() if residual is not None else torch.zeros(total, H, device=src.device)
+    any_addend = False
+    for x in (x1, x2):
+        if x is not None:
+            z = z + x.float().view(total, H)
+            any_addend = True
+    if routed is not None:
+        y, pos, k = routed
+        acc = torch.zeros_like(z)
+        pos = pos.view(total, k).long()
+        for j in range(k):
+            acc = acc + y[pos[:, j]].float()
+        z = z + acc
+        any_addend = True
+    if table is not None:
+        z = z + table[ids[:total].long()].float()
+        any_addend = True
+    if vec is not None:
+        z = z + vec.float()
+        any_addend = True
+    if rows is None and residual is not None and any_addend:
+        residual.view(total, H).copy_(z)
+    if rows is not None:
+        z = z[rows.long()]
+    if out is not None:
+        if norm is not None:
+            _, w, b, alpha = norm
+            z = torch.tanh(alpha.float() * z) * w.float() + b.float()
+        out.view(z.shape).copy_(z.to(out.dtype))
+
+
+def head_gate(o, gates):
+    o.copy_((o.float() * torch.sigmoid(gates.float())[:, :, None]).to(o.dtype))
+
+
+def table_route(token_ids, table, n_experts, ids, weights):
+    T, k = ids.shape
+    ids.copy_(table[token_ids[:T].long()].clamp(0, n_experts - 1))
+    weights.fill_(1.0 / k)
+
+
+def scale_(x, s):
+    x.mul_(s)
+
+
+def linear(x, w, out, bias=None):
+    y = x.float() @ w.float().T
+    if bias is not None:
+        y = y + bias.float()
+    out.copy_(y.to(out.dtype))
+
+
+ALL = ["stream_add_norm", "head_gate", "table_route", "scale_", "sparse_score_fits", "moe_small_fits", "copy_tokens", "sparse_select", "embedding_gather", "add_rmsnorm", "add_rmsnorm_routes", "act_and_mul", "cast", "table_update", "norm_rope_store",
        "paged_attention", "router_topk", "moe_permute", "moe_route", "moe_route_fits", "linear", "attention_tc_fits", "attention_tc_few_fits", "moe_gemm1_gather_fits", "moe_gather", "moe_gemm1_act", "moe_gemm2",
        "moe_combine", "sample"]
 

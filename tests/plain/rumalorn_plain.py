@@ -41,10 +41,12 @@ def distance_bias(rel: torch.Tensor, q_pos: Sequence[int], n_keys: int, max_dist
     """``[heads, queries, keys]`` bias from the table ``rel [buckets, heads]`` (future keys get 0 here;
     the causal mask removes them)."""
     B, H = rel.shape
+    far = max(q_pos) + 1
+    row_of = torch.tensor([distance_bucket(n, B, max_distance) for n in range(far)])  # by distance
     out = torch.zeros(H, len(q_pos), n_keys, dtype=rel.dtype)
     for a, i in enumerate(q_pos):
-        for j in range(min(i + 1, n_keys)):
-            out[:, a, j] = rel[distance_bucket(i - j, B, max_distance)]
+        n = min(i + 1, n_keys)
+        out[:, a, :n] = rel[row_of[i - torch.arange(n)]].T
     return out
 
 

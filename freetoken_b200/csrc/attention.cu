@@ -498,6 +498,12 @@ __global__ void __launch_bounds__(128) attention_bf16_kernel(AttnParams p) {
     // mask, running max
     const int c0 = it.kb + iter * kBN;
     float mx0 = -INFINITY, mx1 = -INFINITY;
+    // a key tile that lies as far behind every row of the warp as the bias table's last entry reaches has one
+    // bias per row; the others look every key's distance up
+    const int far_from = c0 + kBN - 1 + p.dist_len - 1;
+    const bool far = p.dist_bias && __all_sync(0xffffffffu, (!brow0 || qp0 >= far_from) && (!brow1 || qp1 >= far_from));
+    const float fb0 = far && brow0 ? __ldg(brow0 + p.dist_len - 1) * kLog2e : 0.f;
+    const float fb1 = far && brow1 ? __ldg(brow1 + p.dist_len - 1) * kLog2e : 0.f;
 #pragma unroll
     for (int n = 0; n < kBN / 8; ++n) {
 #pragma unroll
@@ -506,8 +512,8 @@ __global__ void __launch_bounds__(128) attention_bf16_kernel(AttnParams p) {
         const bool in = key < it.ke;
         const bool v0 = in && key <= qp0 && key >= lo0;
         const bool v1 = in && key <= qp1 && key >= lo1;
-        s[n][e] = v0 ? s[n][e] * sl2 + dist_bias_at(brow0, p.dist_len, qp0 - key) * kLog2e : -INFINITY;
-        s[n][2 + e] = v1 ? s[n][2 + e] * sl2 + dist_bias_at(brow1, p.dist_len, qp1 - key) * kLog2e : -INFINITY;
+        s[n][e] = v0 ? s[n][e] * sl2 + (far ? fb0 : dist_bias_at(brow0, p.dist_len, qp0 - key) * kLog2e) : -INFINITY;
+        s[n][2 + e] = v1 ? s[n][2 + e] * sl2 + (far ? fb1 : dist_bias_at(brow1, p.dist_len, qp1 - key) * kLog2e) : -INFINITY;
         mx0 = fmaxf(mx0, s[n][e]);
         mx1 = fmaxf(mx1, s[n][2 + e]);
       }
@@ -752,12 +758,18 @@ __global__ void __launch_bounds__(128) attention_decode_bf16_kernel(AttnParams p
     float mx0 = -INFINITY, mx1 = -INFINITY;
     // a 16-key slice that every row of the tile may read in full needs no mask (rows beyond the
     // tile's last are never stored, so what they compute does not matter)
-    const bool interior = p.window == 0 && !p.sel && !p.dist_bias && c0 + 16 <= it.ke && c0 + 16 <= pos_base + 1;
+    // with a bias by distance: a slice that lies as far behind every row as the table's last entry reaches has one
+    // bias per row (all but the last slices of a decode step); the others look every key's distance up
+    const int far_from = c0 + 15 + p.dist_len - 1;
+    const bool far = p.dist_bias && __all_sync(0xffffffffu, (!brow0 || qp0 >= far_from) && (!brow1 || qp1 >= far_from));
+    const float fb0 = far && brow0 ? __ldg(brow0 + p.dist_len - 1) * kLog2e : 0.f;
+    const float fb1 = far && brow1 ? __ldg(brow1 + p.dist_len - 1) * kLog2e : 0.f;
+    const bool interior = p.window == 0 && !p.sel && (!p.dist_bias || far) && c0 + 16 <= it.ke && c0 + 16 <= pos_base + 1;
     if (interior) {
 #pragma unroll
       for (int n = 0; n < 2; ++n) {
-#pragma unroll
-        for (int e = 0; e < 4; ++e) s[n][e] *= sl2;
+        s[n][0] = fmaf(s[n][0], sl2, fb0); s[n][1] = fmaf(s[n][1], sl2, fb0);
+        s[n][2] = fmaf(s[n][2], sl2, fb1); s[n][3] = fmaf(s[n][3], sl2, fb1);
         mx0 = fmaxf(mx0, fmaxf(s[n][0], s[n][1]));
         mx1 = fmaxf(mx1, fmaxf(s[n][2], s[n][3]));
       }
@@ -954,8 +966,11 @@ static int paged_attention_tc_impl(const void* q, const void* k_slab, const void
                                    int n_segs, const int32_t* items, int n_items, float* part_o, float* part_ml,
                                    int n_slots, void* out, int n_tokens, int n_q_heads, int n_kv_heads,
                                    int head_dim, int page_size, int num_pages, float scale, int window,
-                                   void* stream, TcForm form) {
+                                   void* stream, TcForm form, const FtkAttnExtras* extras = nullptr) {
   const bool pair = form == kTcPair, few = form == kTcFew;
+  FTK_REQUIRE(!(extras && extras->dist_bias) || (form != kTcPair && extras->dist_len >= 1 && scale > 0.f),
+              "paged_attention_tc: a distance bias goes with tiles of 128 or of at most 16 rows, a positive scale and a table of "
+              "one entry at least");
   FTK_REQUIRE(q && k_slab && v_slab && block_table && seg_info && items && out, "paged_attention_tc: null pointer");
   FTK_REQUIRE(n_q_heads >= 1 && n_kv_heads >= 1 && n_q_heads % n_kv_heads == 0, "paged_attention_tc: %d query heads, %d KV heads",
               n_q_heads, n_kv_heads);
@@ -979,8 +994,12 @@ static int paged_attention_tc_impl(const void* q, const void* k_slab, const void
   p.Hq = n_q_heads; p.Hkv = n_kv_heads; p.G = n_q_heads / n_kv_heads; p.D = head_dim; p.P = page_size;
   p.num_pages = num_pages; p.tile_rows = pair ? 2 * kTcRows : few ? kTcFewRows : kTcRows; p.scale = scale; p.window = window;
   p.sel = nullptr; p.sel_stride = 0; p.block_size = 0; p.arrivals = nullptr;
-  p.dist_bias = nullptr; p.dist_len = 0;
+  p.dist_bias = extras ? extras->dist_bias : nullptr;
+  p.dist_len = extras ? extras->dist_len : 0;
   cudaStream_t s = (cudaStream_t)stream;
+  if (p.dist_bias) note_variant(few ? "attention: tcgen05, tiles of at most 16 rows, bias by distance"
+                                    : "attention: tcgen05, 128-row query tiles, bias by distance");
+  else
   note_variant(pair ? "attention: tcgen05, two 128-row query tiles per CTA"
                : few ? "attention: tcgen05, tiles of at most 16 rows, one softmax warp"
                      : "attention: tcgen05, 128-row query tiles");
@@ -1007,6 +1026,17 @@ extern "C" int ftk_paged_attention_tc(const void* q, const void* k_slab, const v
   return paged_attention_tc_impl(q, k_slab, v_slab, block_table, bt_stride, seg_info, n_segs, items, n_items, part_o,
                                  part_ml, n_slots, out, n_tokens, n_q_heads, n_kv_heads, head_dim, page_size, num_pages,
                                  scale, window, stream, kTcSingle);
+}
+
+extern "C" int ftk_paged_attention_tc_ex(const void* q, const void* k_slab, const void* v_slab,
+                                         const int32_t* block_table, int bt_stride, const int32_t* seg_info,
+                                         int n_segs, const int32_t* items, int n_items, float* part_o, float* part_ml,
+                                         int n_slots, void* out, int n_tokens, int n_q_heads, int n_kv_heads,
+                                         int head_dim, int page_size, int num_pages, float scale, int window,
+                                         const FtkAttnExtras* extras, int few_rows, void* stream) {
+  return paged_attention_tc_impl(q, k_slab, v_slab, block_table, bt_stride, seg_info, n_segs, items, n_items, part_o,
+                                 part_ml, n_slots, out, n_tokens, n_q_heads, n_kv_heads, head_dim, page_size, num_pages,
+                                 scale, window, stream, few_rows ? kTcFew : kTcSingle, extras);
 }
 
 extern "C" int ftk_paged_attention_tc_pair(const void* q, const void* k_slab, const void* v_slab,

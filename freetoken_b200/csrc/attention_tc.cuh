@@ -155,6 +155,7 @@ __device__ __forceinline__ uint32_t tc_pack(float lo, float hi) {
 
 // Softmax and epilogue of a tile's rows 0..15 by one warp (the warp of TMEM lanes 0..31), for tiles
 // that have no more rows: thread t has rows t / 4 and t / 4 + 8 and a quarter of their columns.
+template <bool BIASED>
 __device__ __forceinline__ void attention_tc_few_rows(const AttnParams& p, uint32_t tmem, int lane, int n_work, int n_rounds,
                                                       uint64_t* s_full, uint64_t* s_empty, uint64_t* p_full,
                                                       uint64_t* pv_done, uint64_t* o_free, volatile int* abortp,
@@ -179,6 +180,11 @@ __device__ __forceinline__ void attention_tc_few_rows(const AttnParams& p, uint3
     // last key a row may read; rows that the tile does not have are never stored and need no mask
     const int hi_a = ra < R ? min(it.ke - 1, pos_base + ra / G) : 0x7fffffff;
     const int hi_b = rb < R ? min(it.ke - 1, pos_base + rb / G) : 0x7fffffff;
+    // a learned bias by distance (see AttnParams::dist_bias): the rows of this thread's two heads
+    const float* brow_a = (BIASED && ra < R) ? p.dist_bias + (size_t)(kvh * G + ra % G) * p.dist_len : nullptr;
+    const float* brow_b = (BIASED && rb < R) ? p.dist_bias + (size_t)(kvh * G + rb % G) * p.dist_len : nullptr;
+    const int qpos_a = pos_base + ra / G, qpos_b = pos_base + rb / G;
+    const float unscale = BIASED ? 1.f / p.scale : 0.f;
     float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int g = g0 + j, sb = g & 1;
@@ -207,6 +213,29 @@ __device__ __forceinline__ void attention_tc_few_rows(const AttnParams& p, uint3
           if (c + 1 > hi_b) v[4 * q + 3] = -INFINITY;
         }
       }
+      float tb_a = 0.f, tb_b = 0.f;  // what every score of this tile gets added per row, in the exp2 domain
+      if constexpr (BIASED) {
+        // a tile that lies as far behind every row as the table's last entry reaches has one bias per row
+        // (all but the last tiles of a decode step); the others look every key's distance up
+        const int last = p.dist_len - 1, far_from = key0 + kTcKeys - 1 + last;
+        if (__all_sync(0xffffffffu, (!brow_a || qpos_a >= far_from) && (!brow_b || qpos_b >= far_from))) {
+          tb_a = brow_a ? __ldg(brow_a + last) * 1.4426950408889634f : 0.f;
+          tb_b = brow_b ? __ldg(brow_b + last) * 1.4426950408889634f : 0.f;
+        } else {
+#pragma unroll
+          for (int q = 0; q < 16; ++q) {
+            const int c = key0 + 8 * q + 2 * cq;
+            if (brow_a) {
+              v[4 * q] += __ldg(brow_a + min(max(qpos_a - c, 0), last)) * unscale;
+              v[4 * q + 1] += __ldg(brow_a + min(max(qpos_a - c - 1, 0), last)) * unscale;
+            }
+            if (brow_b) {
+              v[4 * q + 2] += __ldg(brow_b + min(max(qpos_b - c, 0), last)) * unscale;
+              v[4 * q + 3] += __ldg(brow_b + min(max(qpos_b - c - 1, 0), last)) * unscale;
+            }
+          }
+        }
+      }
       float mx_a = -INFINITY, mx_b = -INFINITY;
 #pragma unroll
       for (int q = 0; q < 16; ++q) {
@@ -215,8 +244,8 @@ __device__ __forceinline__ void attention_tc_few_rows(const AttnParams& p, uint3
       }
       mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
       mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
-      mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2)) * sl2;  // the scale is positive
-      mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2)) * sl2;
+      mx_a = fmaf(fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2)), sl2, tb_a);  // the scale is positive
+      mx_b = fmaf(fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2)), sl2, tb_b);
       // move a row's running maximum only when it grew by more than 8 (or is not set yet)
       float al_a = 1.f, al_b = 1.f;
       if (mx_a > m_a + 8.f || (m_a == -INFINITY && mx_a > -INFINITY)) {
@@ -258,7 +287,7 @@ __device__ __forceinline__ void attention_tc_few_rows(const AttnParams& p, uint3
         }
         tmem_st_wait();
       }
-      const float mb_a = m_a == -INFINITY ? 0.f : m_a, mb_b = m_b == -INFINITY ? 0.f : m_b;
+      const float mb_a = (m_a == -INFINITY ? 0.f : m_a) - tb_a, mb_b = (m_b == -INFINITY ? 0.f : m_b) - tb_b;
       float sum_a = 0.f, sum_b = 0.f;
       // probabilities as bfloat16 pairs into rows 0..15 of the A operand in tensor memory
       const uint32_t p_addr = tmem + (uint32_t)(kTcPCol + sb * (kTcKeys / 2));
@@ -349,7 +378,7 @@ __device__ __forceinline__ void attention_tc_few_rows(const AttnParams& p, uint3
   }
 }
 
-template <bool FEW>
+template <bool FEW, bool BIASED = false>
 __global__ void __launch_bounds__(kTcThreads)
 attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                     const __grid_constant__ CUtensorMap map_v, AttnParams p) {
@@ -421,7 +450,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     // warp instruction issues a whole tile and every lane looks its own page up.  (One thread issuing
     // the boxes of a tile one after the other took longer than the tile's products; keys and values in
     // one warp made the keys wait for the value stage.)
-    if (lane < 16) {
+    // Values that are the keys (one slab given for both): the key tile serves both products.  The value loader
+    // has nothing to do, and a key stage is free again once the second product has read it.
+    if (lane < 16 && !(warp == 6 && p.k == p.v)) {
       const int kv = warp == 6, box = lane >> 1, h = lane & 1;
       const CUtensorMap* map = kv ? &map_v : &map_k;
       uint64_t* full = kv ? v_full : k_full;
@@ -500,6 +531,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     // ------------------------------------------------------------ MMA issuer (lane 0); the warp zeroes value rows past the end
     constexpr uint32_t idesc_qk = instr_desc(kTcKeys);
     constexpr uint32_t idesc_pv = instr_desc(kTcD) | (1u << 16);  // B (values) MN-major
+    const bool tied = p.k == p.v;  // the value tile is the key tile (same boxes, same layout in shared memory)
+    const int v_tile0 = tied ? 1 : 1 + kTcStages;  // first value stage, in tiles from `tiles`
     bool ok = true;
     int g0 = 0;  // tiles of the pieces before this one
     int qi = 0;  // pieces with tiles before this one
@@ -532,7 +565,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
               const uint64_t b = smem_desc(k_s + ks * kTcTile + (kk >> 2) * kTcHalf) + 2 * (kk & 3);
               tc_mma(d, a, b, idesc_qk, kk != 0);
             }
-            tc_commit(&k_empty[ks]);
+            if (!tied) tc_commit(&k_empty[ks]);
             tc_commit(&s_full[st]);
             if (j == n_tiles - 1) tc_commit(&q_empty);  // the next piece's queries may come
           }
@@ -541,7 +574,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         if (j >= 1) {
           const int i = j - 1, g = g0 + i, st = g & 1, vs = g % kTcStages;  // probability buffer, value stage
           const uint32_t par = (g >> 1) & 1;
-          if (!mbar_wait2(&p_full[st], par, &v_full[vs], (uint32_t)(g / kTcStages) & 1u, abortp) ||
+          // (tied values: the stage's keys have been waited for before the first product)
+          if (!(tied ? mbar_wait(&p_full[st], par, abortp)
+                     : mbar_wait2(&p_full[st], par, &v_full[vs], (uint32_t)(g / kTcStages) & 1u, abortp)) ||
               (i == 0 && !mbar_wait(&o_free, (uint32_t)(qi & 1) ^ 1u, abortp))) {  // the piece before has read its output
             if (lane == 0) fail(205);
             ok = false;
@@ -554,7 +589,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             // the last loaded box) and whatever the stage held before (boxes that were not loaded)
             for (int x = lane; x < (kTcKeys - live) * 16; x += 32) {
               const int r = live + x / 16, h = (x / 8) & 1, c = x & 7;
-              *reinterpret_cast<uint4*>(tiles + (1 + kTcStages + vs) * kTcTile + h * kTcHalf + r * 128 + c * 16) =
+              *reinterpret_cast<uint4*>(tiles + (v_tile0 + vs) * kTcTile + h * kTcHalf + r * 128 + c * 16) =
                   make_uint4(0u, 0u, 0u, 0u);
             }
             fence_async_smem();
@@ -566,10 +601,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 #pragma unroll
             for (int kk = 0; kk < 8; ++kk) {  // 16 keys per MMA
               const uint32_t a = tmem + (uint32_t)(kTcPCol + st * (kTcKeys / 2) + kk * 8);
-              const uint64_t b = smem_desc_mn(v_s + vs * kTcTile + kk * 2048, kTcHalf);
+              const uint64_t b = smem_desc_mn((tied ? k_s : v_s) + vs * kTcTile + kk * 2048, kTcHalf);
               tc_mma_ts(d, a, b, idesc_pv, (i | kk) != 0);
             }
-            tc_commit(&v_empty[vs]);
+            tc_commit(tied ? &k_empty[vs] : &v_empty[vs]);
             tc_commit(&pv_done[st]);
           }
           __syncwarp();
@@ -581,7 +616,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   } else if (FEW) {
     // ------------------------------------------------------------ softmax and epilogue of rows 0..15 by one warp
     if ((warp & 3) == 0) {
-      attention_tc_few_rows(p, tmem, lane, n_work, n_rounds, s_full, s_empty, p_full, pv_done, &o_free, abortp, &abort_flag);
+      attention_tc_few_rows<BIASED>(p, tmem, lane, n_work, n_rounds, s_full, s_empty, p_full, pv_done, &o_free, abortp, &abort_flag);
     }
   } else {
     // ------------------------------------------------------------ softmax and epilogue (warps 2..5), one row per thread
@@ -602,6 +637,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     const int qpos = r < R ? pos_base + r / G : -1;
     // last key this row may read; rows past the tile's last are never stored and must not hold the others up
     const int hi = r < R ? min(it.ke - 1, qpos) : 0x7fffffff;
+    // a learned bias by distance (see AttnParams::dist_bias): the row of this thread's head, and the factor that
+    // turns a bias into raw-score units (the scores are scaled after the maximum is taken)
+    const float* brow = (BIASED && r < R) ? p.dist_bias + (size_t)(kvh * G + r % G) * p.dist_len : nullptr;
+    const float unscale = BIASED ? 1.f / p.scale : 0.f;
     float m_used = -INFINITY, l = 0.f;
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int g = g0 + j, sb = g & 1;
@@ -634,10 +673,28 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           if (key0 + 96 + i > hi) v3[i] = -INFINITY;
         }
       }
+      float tile_bias = 0.f;  // what every score of this tile and row gets added, in the exp2 domain
+      if constexpr (BIASED) {
+        // a tile whose nearest key is as far from every row of the warp as the table's last entry reaches has
+        // one bias per row (most tiles of a long prompt); the others look every key's distance up
+        const int nearest = qpos - (key0 + kTcKeys - 1);
+        if (__all_sync(0xffffffffu, brow == nullptr || nearest >= p.dist_len - 1)) {
+          tile_bias = brow ? __ldg(brow + p.dist_len - 1) * 1.4426950408889634f : 0.f;
+        } else if (brow) {
+          const int d0 = qpos - key0, last = p.dist_len - 1;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            v0[i] += __ldg(brow + min(max(d0 - i, 0), last)) * unscale;
+            v1[i] += __ldg(brow + min(max(d0 - 32 - i, 0), last)) * unscale;
+            v2[i] += __ldg(brow + min(max(d0 - 64 - i, 0), last)) * unscale;
+            v3[i] += __ldg(brow + min(max(d0 - 96 - i, 0), last)) * unscale;
+          }
+        }
+      }
       float mx = -INFINITY;
 #pragma unroll
       for (int i = 0; i < 32; ++i) mx = fmaxf(fmaxf(mx, v0[i]), fmaxf(v1[i], fmaxf(v2[i], v3[i])));
-      mx *= sl2;  // the scale is positive: the largest score stays the largest
+      mx = fmaf(mx, sl2, tile_bias);  // the scale is positive: the largest score stays the largest
       // move the running maximum only when it grew by more than 8 (or is not set yet)
       float alpha = 1.f;
       if (mx > m_used + 8.f || (m_used == -INFINITY && mx > -INFINITY)) {
@@ -669,7 +726,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           tmem_st32(lane_addr + 2 * kTcKeys + c * 32, o);
         }
       }
-      const float mb = m_used == -INFINITY ? 0.f : m_used;
+      const float mb = (m_used == -INFINITY ? 0.f : m_used) - tile_bias;
       float sum = 0.f;
       // probabilities as bfloat16 into this row of the A operand in tensor memory: two keys per 32-bit
       // column, 64 columns per buffer behind the output accumulator
@@ -784,7 +841,9 @@ inline int launch_attention_tc(const AttnParams& p, int n_tokens, cudaStream_t s
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(attention_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmem) != cudaSuccess ||
-        cudaFuncSetAttribute(attention_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmem) != cudaSuccess)
+        cudaFuncSetAttribute(attention_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmem) != cudaSuccess ||
+        cudaFuncSetAttribute(attention_tc_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmem) != cudaSuccess ||
+        cudaFuncSetAttribute(attention_tc_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmem) != cudaSuccess)
       return 2;
     configured = true;
   }
@@ -812,8 +871,12 @@ inline int launch_attention_tc(const AttnParams& p, int n_tokens, cudaStream_t s
   }
   const long long n_work = (long long)p.n_items * p.Hkv;  // one CTA per SM, each takes every sms-th piece of work
   const int grid = (int)(n_work < sms ? n_work : sms);
-  if (p.tile_rows == kTcFewRows) {
+  if (p.tile_rows == kTcFewRows && p.dist_bias) {
+    FTK_LAUNCH((attention_tc_kernel<true, true>), grid, kTcThreads, kTcSmem, s, mq, mk, mv, p);
+  } else if (p.tile_rows == kTcFewRows) {
     FTK_LAUNCH(attention_tc_kernel<true>, grid, kTcThreads, kTcSmem, s, mq, mk, mv, p);
+  } else if (p.dist_bias) {
+    FTK_LAUNCH((attention_tc_kernel<false, true>), grid, kTcThreads, kTcSmem, s, mq, mk, mv, p);
   } else {
     FTK_LAUNCH(attention_tc_kernel<false>, grid, kTcThreads, kTcSmem, s, mq, mk, mv, p);
   }

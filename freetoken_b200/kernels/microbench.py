@@ -7,6 +7,8 @@
     python -m freetoken_b200.kernels.microbench few --tokens 1
     python -m freetoken_b200.kernels.microbench sparse --batch 8 --context 32768
     python -m freetoken_b200.kernels.microbench sparse --prefill 2048 --context 32768
+    python -m freetoken_b200.kernels.microbench attention --prefill 2048 --tied --dist-bias 200
+    python -m freetoken_b200.kernels.microbench rows --tokens 2048 --hidden 3072
 
 Each case allocates its inputs once (larger than L2 where the real workload is), warms up, then
 times ``--iters`` launches with CUDA events and prints one JSON line: time, the bytes the kernel has
@@ -117,7 +119,10 @@ def bench_attention(a) -> dict:
     n_pages = sum(-(-kv // P) for _, kv in segs) + 1
     g = torch.Generator(device=dev).manual_seed(0)
     ks = torch.empty(n_pages, Hkv, P, D, dtype=torch.bfloat16, device=dev).normal_(0, 1, generator=g)
-    vs = torch.empty(n_pages, Hkv, P, D, dtype=torch.bfloat16, device=dev).normal_(0, 1, generator=g)
+    tied = bool(getattr(a, "tied", False))  # the values are the keys: one slab, read once where the kernel can
+    vs = ks if tied else torch.empty(n_pages, Hkv, P, D, dtype=torch.bfloat16, device=dev).normal_(0, 1, generator=g)
+    n_bias = int(getattr(a, "dist_bias", 0) or 0)  # entries per head of a bias by distance
+    bias = torch.randn(Hq, n_bias, device=dev, generator=g) if n_bias else None
     width = max(-(-kv // P) for _, kv in segs)
     bt = torch.zeros(len(segs), width, dtype=torch.int32)
     info, q0, page = [], 0, 1
@@ -132,7 +137,7 @@ def bench_attention(a) -> dict:
     q = torch.randn(q0, Hq, D, device=dev, generator=g).to(torch.bfloat16)
     fixed = None
     tile = 128 if (a.prefill >= 128 and not a.no_tc and ops.attention_tc_fits(D, P, G)) else 64
-    if tile == 128 and a.pair:
+    if tile == 128 and a.pair and bias is None:
         tile = 256  # two query tiles per CTA
     few_rows = False
     if not a.prefill:
@@ -153,13 +158,63 @@ def bench_attention(a) -> dict:
         pm = torch.empty(plan.n_slots, Hkv, tile, 2, dtype=torch.float32, device=dev)
     out = torch.empty_like(q)
     us = _time(lambda: ops.paged_attention(q, ks, vs, bt, seg, len(segs), items, plan.n_items, po, pm, out, tile,
-                                           D ** -0.5, None, few_rows=few_rows), a.iters, a.warmup, a.profile)
-    kv_bytes = sum(kv for _, kv in segs) * Hkv * D * 2 * 2
+                                           D ** -0.5, None, few_rows=few_rows, dist_bias=bias), a.iters, a.warmup,
+               a.profile)
+    kv_bytes = sum(kv for _, kv in segs) * Hkv * D * 2 * (1 if tied else 2)
     flops = sum(4 * (ql * kv - ql * (ql - 1) // 2) * Hq * D for ql, kv in segs)
-    return {"us": round(us, 2), "items": plan.n_items, "est_us": None if plan.est_us is None else round(plan.est_us, 1),
-            "kv_bytes": kv_bytes, "gbs": round(kv_bytes / us / 1e3, 1),
+    return {"us": round(us, 2), "tile_rows": tile, "tied": tied, "dist_bias": n_bias, "items": plan.n_items,
+            "est_us": None if plan.est_us is None else round(plan.est_us, 1), "kv_bytes": kv_bytes, "gbs": round(kv_bytes / us / 1e3, 1),
             "hbm_frac": round(kv_bytes / us / 1e3 / HBM_GBS, 3), "tflops": round(flops / us / 1e6, 1),
             "tensor_frac": round(flops / us / 1e6 / BF16_TFLOPS, 3)}
+
+
+def bench_rows(a) -> dict:
+    """The row-wise kernels around the 32-bit stream: RMSNorm with the residual sum, Dynamic Tanh with two
+    addends (a parallel layer's), and the head store with norm + rotation or with bias + position factor."""
+    dev = "cuda"
+    T, H = a.tokens, a.hidden
+    Hq, Hkv, D, P = a.q_heads, a.kv_heads, a.head_dim, 16
+    g = torch.Generator(device=dev).manual_seed(0)
+    bf = torch.bfloat16
+    res = torch.randn(T, H, device=dev, generator=g)
+    x1, x2 = (torch.randn(T, H, device=dev, generator=g).to(bf) for _ in range(2))
+    out = torch.empty(T, H, dtype=bf, device=dev)
+    w, b, alpha = torch.ones(H, device=dev), torch.zeros(H, device=dev), torch.full((1,), 0.5, device=dev)
+    results = {}
+
+    def add(name, fn, nbytes):
+        us = _time(fn, a.iters, a.warmup, a.profile)
+        results[name] = {"us": round(us, 2), "bytes": nbytes, "gbs": round(nbytes / us / 1e3, 1),
+                         "hbm_frac": round(nbytes / us / 1e3 / HBM_GBS, 3)}
+
+    add("add_rmsnorm", lambda: ops.add_rmsnorm(x1, res, w, 1e-6, False, out), T * H * (4 + 4 + 2 + 2))
+    add("stream_add_norm (dynamic tanh, two addends)",
+        lambda: ops.stream_add_norm(res, out, x1=x1, x2=x2, norm=("dynamic_tanh", w, b, alpha)), T * H * (4 + 4 + 2 + 2 + 2))
+    rows = (Hq + 2 * Hkv) * D
+    qkv = torch.randn(T, rows, device=dev, generator=g).to(bf)
+    q = torch.empty(T, Hq, D, dtype=bf, device=dev)
+    n_pages = -(-T // P) + 1
+    slab_k, slab_v = (torch.zeros(n_pages, Hkv, P, D, dtype=bf, device=dev) for _ in range(2))
+    slots = torch.arange(P, P + T, dtype=torch.int32, device=dev)
+    positions = torch.arange(T, dtype=torch.int32, device=dev)
+    rd = D // 2
+    table = torch.randn(T, rd, device=dev, generator=g)
+    nw = torch.ones(D, device=dev)
+    add("norm_rope_store (norm, rotation, k and v)", lambda: ops.norm_rope_store(qkv, D, rd, positions, table, 1e-6, False, [
+        dict(first_head=0, n_heads=Hq, norm_weight=nw, rotate=True, dense_out=q),
+        dict(first_head=Hq, n_heads=Hkv, norm_weight=nw, rotate=True, slab=slab_k, slot_map=slots),
+        dict(first_head=Hq + Hkv, n_heads=Hkv, norm_weight=None, rotate=False, slab=slab_v, slot_map=slots)]),
+        T * (Hq + 2 * Hkv) * D * 2 * 2)
+    qb, kb = torch.randn(Hq * D, device=dev, generator=g), torch.randn(Hkv * D, device=dev, generator=g)
+    factors = torch.rand(T, device=dev, generator=g) + 1
+    add("norm_rope_store (bias, position factor, k only)", lambda: ops.norm_rope_store(qkv, D, 0, positions, None, 0.0, False, [
+        dict(first_head=0, n_heads=Hq, norm_weight=None, rotate=False, dense_out=q, bias=qb, pos_scale=factors),
+        dict(first_head=Hq, n_heads=Hkv, norm_weight=None, rotate=False, slab=slab_k, slot_map=slots, bias=kb)]),
+        T * (Hq + Hkv) * D * 2 * 2)
+    o = torch.randn(T, Hq, D, device=dev, generator=g).to(bf)
+    gates = torch.randn(T, Hq, device=dev, generator=g).to(bf)
+    add("head_gate", lambda: ops.head_gate(o, gates), T * Hq * D * 2 * 2)
+    return results
 
 
 def bench_few(a) -> dict:
@@ -277,7 +332,7 @@ def bench_sample(a) -> dict:
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="microbench")
     sub = ap.add_subparsers(dest="case", required=True)
-    for name in ("moe", "attention", "sample", "sparse", "few"):
+    for name in ("moe", "attention", "sample", "sparse", "few", "rows"):
         p = sub.add_parser(name)
         p.add_argument("--iters", type=int, default=20)
         p.add_argument("--warmup", type=int, default=5)
@@ -306,6 +361,14 @@ def main(argv=None) -> int:
             p.add_argument("--few-rows", action="store_true",
                            help="decode on the tcgen05 kernel in its form for tiles of at most 16 rows")
             p.add_argument("--pair", action="store_true", help="prefill on the tcgen05 kernel with two query tiles per CTA")
+            p.add_argument("--tied", action="store_true", help="the values are the keys (one slab)")
+            p.add_argument("--dist-bias", type=int, default=0, help="entries per head of a bias by distance (0 = none)")
+        elif name == "rows":
+            p.add_argument("--tokens", type=int, default=2048)
+            p.add_argument("--hidden", type=int, default=3072)
+            p.add_argument("--q-heads", type=int, default=48)
+            p.add_argument("--kv-heads", type=int, default=8)
+            p.add_argument("--head-dim", type=int, default=128)
         elif name == "few":
             p.add_argument("--tokens", type=int, default=1)
             p.add_argument("--hidden", type=int, default=3072)
@@ -334,7 +397,8 @@ def main(argv=None) -> int:
             p.add_argument("--vocab", type=int, default=200064)
             p.add_argument("--temperature", type=float, default=0.0)
     a = ap.parse_args(argv)
-    res = {"moe": bench_moe, "attention": bench_attention, "sample": bench_sample, "sparse": bench_sparse, "few": bench_few}[a.case](a)
+    res = {"moe": bench_moe, "attention": bench_attention, "sample": bench_sample, "sparse": bench_sparse, "few": bench_few,
+           "rows": bench_rows}[a.case](a)
     print(json.dumps({"case": a.case, **{k: v for k, v in vars(a).items() if k != "case"}, "result": res}))
     return 0
 

@@ -94,6 +94,8 @@ _SIGNATURES = {
     "ftk_attention_tc_fits": [_i, _i, _i],
     "ftk_paged_attention_tc": [_vp, _vp, _vp, _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _i, _vp,
                                _i, _i, _i, _i, _i, _i, _f, _i, _vp],
+    "ftk_paged_attention_tc_ex": [_vp, _vp, _vp, _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _i, _vp,
+                                  _i, _i, _i, _i, _i, _i, _f, _i, ctypes.POINTER(_AttnExtras), _i, _vp],
     "ftk_attention_tc_few_fits": [_i, _i, _i],
     "ftk_paged_attention_tc_few": [_vp, _vp, _vp, _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _i, _vp,
                                       _i, _i, _i, _i, _i, _i, ctypes.c_float, _i, _vp],
@@ -430,7 +432,8 @@ def paged_attention(q: torch.Tensor, k_slab: torch.Tensor, v_slab: torch.Tensor,
     ``dist_bias [Hq, L]`` (float32) adds ``dist_bias[h, min(i - j, L - 1)]`` to the scaled score of query
     position ``i`` and key position ``j`` (a learned bias by distance; not multiplied by ``scale``).
     ``v_slab`` may be ``k_slab`` itself (values that are the keys): each key tile is then brought in once.
-    The tcgen05 kernels take neither.
+    Of the tcgen05 kernels the ones with one query tile a piece (128 rows, or at most 16) take the bias; with
+    one slab for keys and values their key tile in shared memory serves both products.
     """
     T, Hq, D = q.shape
     pages, Hkv, P, D2 = k_slab.shape
@@ -446,9 +449,23 @@ def paged_attention(q: torch.Tensor, k_slab: torch.Tensor, v_slab: torch.Tensor,
         raise KernelError(f"paged_attention: few_rows goes with tiles of 16 rows, got {tile_rows}")
     if tile_rows in (128, 256) or few_rows:
         # bfloat16 steps on the tcgen05 kernels: one query tile per CTA, a pair of them, or tiles of a few rows
-        if sel is not None or window or q.dtype != torch.bfloat16 or dist_bias is not None:
-            raise KernelError("paged_attention: the tcgen05 kernels take bfloat16 without window, block selection "
-                              "or distance bias")
+        if sel is not None or window or q.dtype != torch.bfloat16:
+            raise KernelError("paged_attention: the tcgen05 kernels take bfloat16 without window or block selection")
+        if dist_bias is not None:  # the forms with one query tile a piece (128 rows, or at most 16) take it
+            if tile_rows == 256 or dist_bias.dim() != 2 or dist_bias.shape[0] != Hq:
+                raise KernelError("paged_attention: of the tcgen05 kernels the ones with one query tile a piece take a "
+                                  "distance bias [Hq, L]")
+            ex = _AttnExtras(_dev(dist_bias, "dist_bias", torch.float32), dist_bias.shape[1])
+            _check(_lib().ftk_paged_attention_tc_ex(
+                _dev(q, "q"), _dev(k_slab, "k_slab"), _dev(v_slab, "v_slab"),
+                _dev(block_table, "block_table", torch.int32), block_table.shape[1],
+                _dev(seg_info, "seg_info", torch.int32), n_segs,
+                _dev(items, "items", torch.int32), n_items,
+                _dev(part_o, "part_o", torch.float32), _dev(part_ml, "part_ml", torch.float32), n_slots,
+                _dev(out, "out"), T, Hq, Hkv, D, P, pages, float(scale), 0, ctypes.byref(ex), 1 if few_rows else 0,
+                _stream()),
+                "paged_attention (tcgen05, distance bias)", 2 if n_slots else 1)
+            return
         fn = (_lib().ftk_paged_attention_tc_few if few_rows else
               _lib().ftk_paged_attention_tc_pair if tile_rows == 256 else _lib().ftk_paged_attention_tc)
         _check(fn(

@@ -33,7 +33,7 @@ TC_MIN_DECODE_SPAN = 0   # decode steps go there from this length of the longest
 
 def attention_kernel_form(dtype: torch.dtype, decode_only: bool = False, group: int = 1, n_tokens: int = 0,
                           head_dim: int = 0, page_size: int = 0, window: Optional[int] = None,
-                          longest_span: int = 0) -> Tuple[int, bool]:
+                          longest_span: int = 0, one_tile_only: bool = False) -> Tuple[int, bool]:
     """``(query rows one attention CTA handles, the tcgen05 kernel's form for few rows)``.
 
     16 rows in the 32-bit kernel.  bfloat16 steps whose sizes the tcgen05 kernels take: 128 rows for
@@ -45,7 +45,8 @@ def attention_kernel_form(dtype: torch.dtype, decode_only: bool = False, group: 
     most 16 rows, where one warp takes the softmax (groups of up to 16 heads; ``longest_span`` is the longest
     request's length rounded up to a power of two, from which on they go there:
     ``TC_MIN_DECODE_SPAN``), larger groups to the 128-row kernel.  Otherwise 16 rows for decode steps
-    of small groups and 64 in the bfloat16 mma.sync kernels."""
+    of small groups and 64 in the bfloat16 mma.sync kernels.  ``one_tile_only``: of the tcgen05 kernels only
+    the ones with a single query tile a piece may be chosen (they are the ones that take a bias by distance)."""
     if dtype != torch.bfloat16:
         return 16, False
     sized = bool(window is None and head_dim and page_size)
@@ -57,7 +58,7 @@ def attention_kernel_form(dtype: torch.dtype, decode_only: bool = False, group: 
                 return 128, False
         return (16 if group <= 16 else 64), False
     tc = sized and ops.attention_tc_fits(head_dim, page_size, group)
-    if tc and (n_tokens >= TC_PAIR_MIN_TOKENS or
+    if tc and not one_tile_only and (n_tokens >= TC_PAIR_MIN_TOKENS or
                (n_tokens >= TC_PAIR_MIN_TOKENS_LONG and longest_span >= TC_PAIR_MIN_SPAN)):
         return 256, False
     if tc and n_tokens >= TC_MIN_TOKENS:

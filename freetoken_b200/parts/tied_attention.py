@@ -139,8 +139,9 @@ class TiedKVAttention(Mixer):
 
     # ------------------------------------------------------------------ step
     def kernel_form(self, decode_only: bool, n_tokens: int = 0, page_size: int = 0, longest_span: int = 0):
-        # (no head size and page size given: the tcgen05 kernels take neither a distance bias nor tied values)
-        return attention_kernel_form(self.env.dtype, decode_only, self.group, n_tokens, 0, 0, self.window, longest_span)
+        # (of the tcgen05 kernels the ones with a single query tile a piece take a bias by distance)
+        return attention_kernel_form(self.env.dtype, decode_only, self.group, n_tokens, self.pad_dim, page_size,
+                                     self.window, longest_span, one_tile_only=True)
 
     def plan_key(self, decode_only: bool = False, n_tokens: int = 0, page_size: int = 0, longest_span: int = 0):
         rows, few_rows = self.kernel_form(decode_only, n_tokens, page_size, longest_span)
@@ -148,7 +149,8 @@ class TiedKVAttention(Mixer):
 
     def prepare(self, builder) -> None:
         n_tokens = sum(q for q, _ in builder.seg_lens)
-        rows, few_rows = self.kernel_form(builder.decode_only, n_tokens, 0, builder.longest_span())
+        page_size = builder.engine.config.page_size if builder.engine is not None else 0
+        rows, few_rows = self.kernel_form(builder.decode_only, n_tokens, page_size, builder.longest_span())
         self._step_plan = builder.attention_plan(self.group, rows, self.window, self.n_kv_heads, self.pad_dim, few_rows)
 
     def forward(self, h: torch.Tensor, step: StepState, cache: Any, writes_cache: bool) -> torch.Tensor:
@@ -171,7 +173,7 @@ class TiedKVAttention(Mixer):
         k = cache.slabs["k"]
         ops.paged_attention(q, k, k, cache.block_table, step.seg_info, len(step.segments), plan.items_dev,
                             plan.n_items, plan.part_o, plan.part_ml, o, self._step_plan[2], self.scale, self.window,
-                            dist_bias=self._dist_bias)
+                            few_rows=self._step_plan[6], dist_bias=self._dist_bias)
         if self.gate:
             ops.head_gate(o, qkg[:, self.q_dim + self.kv_dim:])
         out = ws.get("tied.out", (T, self.hidden), dt, (cap, self.hidden))

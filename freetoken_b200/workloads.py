@@ -12,6 +12,13 @@ time of a step at the start and at the end of the prompt.
     python bench.py --workload long_contexts [--layers 16] [--requests 8] [--max-prompt 24576] [--new-tokens 512]
     python bench.py --workload chunked_prefill [--layers 4] [--prompt 131072] [--chunk 512] [--decoders 63]
 
+``designs``: Rumalorn (parallel Dynamic-Tanh layers, key-tied attention with a bias by distance, experts
+named by a table over token ids) beside MiniMax-M3 at equal layer sizes, both with random weights: a
+2 048-token prompt in one step and decode steps of eight requests at 2 048 tokens of context, at a few
+sizes that resemble real models' layers.
+
+    python bench.py --workload designs [--layers 4]
+
 Each prints one JSON line.  The reference times whole generations of this kind in
 benchmarks/bench_decode_moe.py:8-24 (tokens after the first / time between first and last).
 """
@@ -117,7 +124,101 @@ def chunked_prefill(raw: Dict[str, Any], layers: int = 4, prompt: int = 131072, 
     }
 
 
+DESIGN_SIZES = (
+    # name, width, query heads, KV heads, head size, experts, experts per token, expert width, vocabulary
+    ("w1024_h64", 1024, 16, 4, 64, 16, 2, 1408, 32768),
+    ("w2048_h128", 2048, 16, 4, 128, 32, 4, 1024, 32768),
+    ("w3072_h128", 3072, 48, 8, 128, 64, 8, 1536, 65536),
+)
+
+
+def _design_configs(width, heads, kv, dim, experts, top, ff, vocab, layers):
+    mixer = {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "bias_max": 256,
+             "q_temp": {"coef": 0.3, "every": 64}, "buckets": 32}
+    mlp = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top}}
+    ruma = {"architecture": "Rumalorn", "vocab": vocab, "width": width, "logit_scale": 1.0, "norm": {"eps": 1e-5},
+            "layers": [{"type": "attention", "mixer": mixer, "mlp": mlp} for _ in range(layers)]}
+    m3 = {"architectures": ["MiniMaxM3SparseForCausalLM"], "model_type": "minimax_m3", "vocab_size": vocab,
+          "hidden_size": width, "num_hidden_layers": layers, "num_attention_heads": heads, "num_key_value_heads": kv,
+          "head_dim": dim, "rotary_dim": dim // 2, "rope_theta": 5000000.0, "max_position_embeddings": 8192,
+          "rms_norm_eps": 1e-6, "use_qk_norm": True, "use_gemma_norm": True, "tie_word_embeddings": False,
+          "hidden_act": "silu", "num_local_experts": experts, "num_experts_per_tok": top, "intermediate_size": ff,
+          "scoring_func": "sigmoid", "use_routing_bias": True, "routed_scaling_factor": 1.0, "n_shared_experts": 0,
+          "torch_dtype": "bfloat16"}
+    return {"rumalorn": ruma, "minimax_m3": m3}
+
+
+def _time_design(raw: Dict[str, Any], prompt: int, batch: int, steps: int, warmup: int) -> Dict[str, Any]:
+    eng = Engine(EngineConfig(model_path="", dtype="bfloat16", use_dummy_weight=True, seed=0, page_size=16,
+                              max_running_req=batch, num_token_override=(batch + 1) * (prompt + 256),
+                              max_seq_len_override=prompt + 256, max_extend_tokens=prompt, max_step_tokens=prompt),
+                 raw_config=raw)
+    V = eng.spec.vocab_size
+    rng = np.random.default_rng(0)
+
+    def ev():
+        return torch.cuda.Event(enable_timing=True)
+
+    times = []
+    for i in range(3 + 3):  # one prompt in one step
+        toks = rng.integers(0, V, prompt).tolist()
+        a, b = ev(), ev()
+        torch.cuda.synchronize()
+        a.record()
+        eng.step([StepEntry(("p", i), toks, [prompt - 1])])
+        b.record()
+        torch.cuda.synchronize()
+        eng.close(("p", i))
+        if i >= 3:
+            times.append(a.elapsed_time(b))
+    prefill_ms = float(np.median(times))
+    rids = [("d", i) for i in range(batch)]
+    for r in rids:
+        eng.step([StepEntry(r, rng.integers(0, V, prompt).tolist(), [])])
+
+    def one():
+        eng.step([StepEntry(r, [int(rng.integers(0, V))], [0]) for r in rids])
+
+    for _ in range(warmup):
+        one()
+    torch.cuda.synchronize()
+    a, b = ev(), ev()
+    a.record()
+    for _ in range(steps):
+        one()
+    b.record()
+    torch.cuda.synchronize()
+    decode_ms = a.elapsed_time(b) / steps
+    del eng
+    torch.cuda.empty_cache()
+    return {"prefill_ms": round(prefill_ms, 3), "prefill_tokens_per_s": round(prompt / (prefill_ms / 1e3), 1),
+            "decode_ms_per_step": round(decode_ms, 4), "decode_tokens_per_s": round(batch / (decode_ms / 1e3), 1)}
+
+
+def designs(raw: Dict[str, Any], layers: int = 4, prompt: int = 2048, batch: int = 8, steps: int = 32,
+            warmup: int = 8) -> Dict[str, Any]:
+    """``raw`` (the headline configuration) is not used: the sizes are this workload's own."""
+    import gc
+
+    out: Dict[str, Any] = {"workload": "designs", "layers": layers, "prompt": prompt, "decode_batch": batch,
+                           "decode_context": prompt, "steps": steps, "warmup": warmup, "dtype": "bf16",
+                           "data": "synthetic: uniform random token ids, random weights made on the device", "sizes": {}}
+    for name, *dims in DESIGN_SIZES:
+        width, heads, kv, dim, experts, top, ff, vocab = dims
+        row: Dict[str, Any] = {"width": width, "q_heads": heads, "kv_heads": kv, "head_dim": dim, "experts": experts,
+                               "top_k": top, "expert_width": ff, "vocab": vocab}
+        for design, cfg in _design_configs(*dims, layers).items():
+            row[design] = _time_design(cfg, prompt, batch, steps, warmup)
+            gc.collect()
+            torch.cuda.empty_cache()
+        row["rumalorn_over_minimax_m3"] = {
+            "prefill": round(row["rumalorn"]["prefill_tokens_per_s"] / row["minimax_m3"]["prefill_tokens_per_s"], 3),
+            "decode": round(row["rumalorn"]["decode_tokens_per_s"] / row["minimax_m3"]["decode_tokens_per_s"], 3)}
+        out["sizes"][name] = row
+    return out
+
+
 def run(name: str, raw: Dict[str, Any], **kw: Any) -> int:
-    fn = {"long_contexts": long_contexts, "chunked_prefill": chunked_prefill}[name]
+    fn = {"long_contexts": long_contexts, "chunked_prefill": chunked_prefill, "designs": designs}[name]
     print(json.dumps(fn(raw, **{k: v for k, v in kw.items() if v is not None})))
     return 0

@@ -7,6 +7,7 @@ import pytest
 import torch
 
 import kernel_refs as ref
+from freetoken_b200.engine.engine import StepEntry
 from helpers import make_engine, mixed_schedule, model_folder, replay_cuts, replay_mixed, replay_whole, tokens_for
 from plain.rumalorn_plain import PlainRumalorn, dynamic_tanh
 from tiny_rumalorn import ALL, RUMA_1
@@ -17,7 +18,7 @@ from freetoken_b200.kernels import ops
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 DTYPES = [torch.float32, torch.bfloat16]
-PAGE = {"R1": 4, "R2": 8, "R3": 4, "R4": 16}
+PAGE = {"R1": 4, "R2": 8, "R3": 4, "R4": 16, "R5": 16}
 
 
 def rnd(*shape, dtype=torch.float32, scale=1.0, seed=0):
@@ -148,10 +149,13 @@ def attention_problem(dtype, Hq, Hkv, D, P, segs, seed=0, scale_k=1.0):
     return q, ks.to(DEV), bt.to(DEV), torch.tensor(seg_info, dtype=torch.int32, device=DEV)
 
 
-def run_biased(dtype, Hq, Hkv, D, P, segs, dist_bias, tile, fixed_splits=None, force_split=False, q=None, problem=None):
+def run_biased(dtype, Hq, Hkv, D, P, segs, dist_bias, tile, fixed_splits=None, force_split=False, q=None, problem=None,
+               few_rows=False):
     qq, ks, bt, seg = problem or attention_problem(dtype, Hq, Hkv, D, P, segs)
     q = qq if q is None else q
     kw = dict(sm_count=4096, min_split_keys=32) if force_split else dict(sm_count=148)
+    if tile == 128 or few_rows:
+        kw["key_tile"] = 128  # as the engine plans the tcgen05 kernels' work
     plan = build_plan(segs, Hq // Hkv, tile, None, Hkv, fixed_splits=fixed_splits, **kw)
     items = torch.from_numpy(plan.items).to(DEV)
     part_o = part_ml = None
@@ -162,7 +166,7 @@ def run_biased(dtype, Hq, Hkv, D, P, segs, dist_bias, tile, fixed_splits=None, f
     want = torch.empty_like(out)
     scale = 0.8 * D ** -0.5
     ops.paged_attention(q, ks, ks, bt, seg, len(segs), items, plan.n_items, part_o, part_ml, out, tile, scale, None,
-                        dist_bias=dist_bias)
+                        dist_bias=dist_bias, few_rows=few_rows)
     ref.paged_attention(q, ks, ks, bt, seg, len(segs), items, plan.n_items, None, None, want, tile, scale, None,
                         dist_bias=dist_bias)
     return out, want, plan
@@ -190,21 +194,41 @@ def test_attention_with_distance_bias_and_keys_as_values(dtype, Hq, Hkv, D, P, L
     torch.testing.assert_close(out.float(), want.float(), **attn_tol(dtype))
 
 
+@pytest.mark.parametrize("Hq,Hkv,P,L", [(12, 2, 16, 200), (4, 4, 32, 7), (16, 1, 16, 130), (6, 2, 64, 1)])
+def test_attention_with_distance_bias_on_the_tensor_core_kernel(Hq, Hkv, P, L):
+    bias = rnd(Hq, L, seed=3, scale=1.5)
+    for segs, force in (([(300, 300)], False), ([(128, 128), (1, 40), (200, 517), (3, 3)], False), ([(256, 900)], True)):
+        out, want, plan = run_biased(torch.bfloat16, Hq, Hkv, 128, P, segs, bias, 128, force_split=force)
+        assert ops.variant_counts().get("attention: tcgen05, 128-row query tiles, bias by distance", 0) > 0
+        assert not force or plan.n_slots > 0
+        torch.testing.assert_close(out.float(), want.float(), **attn_tol(torch.bfloat16))
+    assert ops.read_status() == 0
+    if Hq // Hkv <= 16:  # steps of single tokens on the same kernel in its form for tiles of at most 16 rows
+        dec = [(1, 1), (1, 130), (1, 128), (1, 129), (1, 1000), (1, 257), (1, L + 127), (1, L + 128), (1, L + 129)]
+        for fixed in (None, 1, 4, 16):
+            out, want, plan = run_biased(torch.bfloat16, Hq, Hkv, 128, P, dec, bias, 16, fixed_splits=fixed, few_rows=True)
+            assert ops.variant_counts().get("attention: tcgen05, tiles of at most 16 rows, bias by distance", 0) > 0
+            torch.testing.assert_close(out.float(), want.float(), **attn_tol(torch.bfloat16))
+        assert ops.read_status() == 0
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("tile", [16, 64])
+@pytest.mark.parametrize("tile", [16, 64, 128, "few"])
 def test_a_bias_that_singles_out_one_distance_picks_that_key(dtype, tile):
     """With queries of zero the scores are the bias alone: +60 at one distance makes the output that key
     (the values are the keys), so a table read one entry off, or clamped one entry early, shows at once."""
-    if dtype == torch.float32 and tile == 64:
+    if dtype == torch.float32 and tile != 16:
         pytest.skip("the 32-bit kernel has 16-row tiles")
-    Hq, Hkv, D, P, L = 4, 2, 32, 8, 24
-    segs = [(40, 100), (1, 90)] if tile == 64 else [(1, 100), (1, 90)]
+    few = tile == "few"  # the tcgen05 kernel's form for tiles of at most 16 rows
+    tile = 16 if few else tile
+    Hq, Hkv, D, P, L = (4, 2, 32, 8, 24) if tile != 128 and not few else (4, 2, 128, 16, 24)
+    segs = [(40, 100), (1, 90)] if tile == 64 else [(1, 100), (1, 90)] if tile == 16 else [(150, 400), (130, 390)]
     problem = attention_problem(dtype, Hq, Hkv, D, P, segs, seed=2)
     q, ks, bt, seg = problem
     for d_star in (0, 1, 7, 8, L - 2):
         bias = torch.zeros(Hq, L, device=DEV)
         bias[:, d_star] = 60.0
-        out, want, _ = run_biased(dtype, Hq, Hkv, D, P, segs, bias, tile, q=torch.zeros_like(q), problem=problem)
+        out, want, _ = run_biased(dtype, Hq, Hkv, D, P, segs, bias, tile, q=torch.zeros_like(q), problem=problem, few_rows=few)
         torch.testing.assert_close(out.float(), want.float(), **attn_tol(dtype))
         for q_start, q_len, kv_len, row in seg.tolist():
             i = kv_len - 1  # the segment's last query
@@ -215,7 +239,7 @@ def test_a_bias_that_singles_out_one_distance_picks_that_key(dtype, tile):
     # the last entry stands for every distance from L - 1 on: the output is the mean of all those keys
     bias = torch.zeros(Hq, L, device=DEV)
     bias[:, L - 1] = 60.0
-    out, want, _ = run_biased(dtype, Hq, Hkv, D, P, segs, bias, tile, q=torch.zeros_like(q), problem=problem)
+    out, want, _ = run_biased(dtype, Hq, Hkv, D, P, segs, bias, tile, q=torch.zeros_like(q), problem=problem, few_rows=few)
     torch.testing.assert_close(out.float(), want.float(), **attn_tol(dtype))
     q_start, q_len, kv_len, row = seg.tolist()[1]
     far = torch.stack([ks[int(bt[row, j // P]), :, j % P].float() for j in range(0, kv_len - 1 - (L - 1) + 1)]).mean(0)
@@ -252,7 +276,7 @@ def test_a_far_key_that_matches_the_query_stands_out(dtype):
 
 # --------------------------------------------------------------------------- the engine against the plain model
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["R1", "R2", "R3", "R4"])
+@pytest.mark.parametrize("name", ["R1", "R2", "R3", "R4", "R5"])
 def test_cuts_and_batches_agree_with_the_plain_model(name, dtype, tmp_path_factory):
     folder = model_folder(tmp_path_factory.getbasetemp(), name, ALL[name])
     plain = PlainRumalorn(folder)
@@ -299,6 +323,27 @@ def test_long_prompt_and_long_decoding(dtype, tmp_path_factory):
     assert_rows(replay_whole(eng, "w", toks), want, dtype, "whole")
     assert_rows(replay_cuts(eng, "d", toks, [320]), want, dtype, "a hundred tokens one by one")
     assert_rows(replay_cuts(eng, "c", toks, [63, 2, 64, 65, 127, 2, 33] + [1] * 20 + [30, 2]), want, dtype, "portions")
+
+
+def test_long_steps_of_heads_of_128_run_the_tensor_core_attention(tmp_path_factory):
+    folder = model_folder(tmp_path_factory.getbasetemp(), "R5", ALL["R5"])
+    plain = PlainRumalorn(folder)
+    toks = tokens_for(plain.vocab, 450, 9)
+    want = plain.logits(toks)
+    eng = make_engine(folder, "bfloat16", DEV, 16, pages=96, max_step=512)
+    ops.variant_counts(reset=True)
+    assert_rows(replay_whole(eng, "w", toks), want, "bfloat16", "whole")
+    assert ops.variant_counts().get("attention: tcgen05, 128-row query tiles, bias by distance", 0) == 3
+    assert_rows(replay_cuts(eng, "c", toks, [200, 130, 2, 100]), want, "bfloat16", "portions, the rest one by one")
+    assert ops.variant_counts().get("attention: tcgen05, tiles of at most 16 rows, bias by distance", 0) > 0
+    others = {f"o{i}": tokens_for(plain.vocab, 20 + i, 20 + i) for i in range(3)}
+    for r, t in others.items():  # three requests that decode beside a long portion
+        eng.step([StepEntry(r, t[:-1], [])])
+    out = eng.step([StepEntry("long", toks[:300], list(range(300)))] + [StepEntry(r, t[-1:], [0]) for r, t in others.items()])
+    assert_rows(out.logits[:300], want[:300], "bfloat16", "a long portion beside single tokens")
+    for i, (r, t) in enumerate(others.items()):
+        assert_rows(out.logits[300 + i:301 + i], plain.logits(t)[-1:], "bfloat16", r)
+    eng.check_kernels()
 
 
 def test_greedy_generation_through_the_scheduler(tmp_path_factory):

@@ -59,3 +59,12 @@ RUMA_4 = {
 }
 
 ALL = {"R1": RUMA_1, "R2": RUMA_2, "R3": RUMA_3, "R4": RUMA_4}
+
+# R5: heads of 128 on pages of 16 tokens: bfloat16 steps of 128 tokens and more run the tcgen05 attention kernel
+_m5 = _mixer(6, 2, 128, 0.09, 100, 0.3, 32, 16)
+RUMA_5 = {
+    "architecture": ARCH, "vocab": 300, "width": 128, "logit_scale": 0.5, "norm": {"eps": 1e-5},
+    "layers": [_layer(_m5, _dense(96, 2.0)), _layer(_m5, _moe(64, 4, 2))],
+    "loop": {"start": 0, "stop": 1, "times": 2},
+}
+ALL["R5"] = RUMA_5

@@ -24,7 +24,7 @@ from freetoken_b200.config.spec import PartSpec
 from freetoken_b200.registry import architecture_of
 
 TOL = dict(rtol=1e-4, atol=2e-5)
-PAGE = {"R1": 4, "R2": 8, "R3": 4, "R4": 16}
+PAGE = {"R1": 4, "R2": 8, "R3": 4, "R4": 16, "R6": 8}
 
 
 @pytest.fixture
@@ -122,7 +122,7 @@ def test_names_shapes_and_table_rows_from_the_file(tmp_path_factory):
 
 
 # --------------------------------------------------------------------------- the engine on the CPU
-@pytest.mark.parametrize("name", ["R1", "R2", "R3", "R4"])
+@pytest.mark.parametrize("name", ["R1", "R2", "R3", "R4", "R6"])
 def test_cuts_and_batches_agree_with_the_plain_model(name, cpu_ops, tmp_path_factory):
     folder = model_folder(tmp_path_factory.getbasetemp(), name, ALL[name])
     plain = PlainRumalorn(folder)
@@ -162,3 +162,18 @@ def test_the_plain_model_notices_a_shifted_bucket_edge_and_a_changed_temperature
         for l in other.cfg["layers"]:
             l["mixer"][key] = value
         assert float((other.logits(toks) - ref).abs().max()) > 100 * TOL["atol"], key
+
+
+def plain_for_the_command_line(folder):
+    """The plain model as the command line's tests take one: ``cfg.vocab`` and float32 ``logits``."""
+    from types import SimpleNamespace
+
+    plain = PlainRumalorn(folder)
+    return SimpleNamespace(cfg=SimpleNamespace(vocab=plain.vocab), logits=lambda toks: plain.logits(toks).float())
+
+
+def test_the_command_line_makes_a_model_generates_and_replays(tmp_path, capsys, cpu_ops):
+    from test_cli import generate_and_replay, make_model
+
+    folder = make_model(tmp_path, RUMA_1, capsys)
+    generate_and_replay(folder, "cpu", "float32", capsys, tmp_path, plain_for_the_command_line(folder))

@@ -18,7 +18,7 @@ from freetoken_b200.kernels import ops
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 DTYPES = [torch.float32, torch.bfloat16]
-PAGE = {"R1": 4, "R2": 8, "R3": 4, "R4": 16, "R5": 16}
+PAGE = {"R1": 4, "R2": 8, "R3": 4, "R4": 16, "R5": 16, "R6": 8}
 
 
 def rnd(*shape, dtype=torch.float32, scale=1.0, seed=0):
@@ -276,7 +276,7 @@ def test_a_far_key_that_matches_the_query_stands_out(dtype):
 
 # --------------------------------------------------------------------------- the engine against the plain model
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["R1", "R2", "R3", "R4", "R5"])
+@pytest.mark.parametrize("name", ["R1", "R2", "R3", "R4", "R5", "R6"])
 def test_cuts_and_batches_agree_with_the_plain_model(name, dtype, tmp_path_factory):
     folder = model_folder(tmp_path_factory.getbasetemp(), name, ALL[name])
     plain = PlainRumalorn(folder)
@@ -396,3 +396,12 @@ def test_the_replay_tool_runs_the_design(tmp_path_factory, tmp_path):
         assert_rows(torch.from_numpy(got[0]), la[[0, 19]], dtype)
         assert_rows(torch.from_numpy(got[1]), torch.stack([la[20], lb[8]]), dtype)
         assert_rows(torch.from_numpy(got[2]), la[[29]], dtype)
+
+
+@pytest.mark.parametrize("name,dtype", [("R1", "float32"), ("R4", "bfloat16")])
+def test_the_command_line_on_the_device(name, dtype, tmp_path, capsys):
+    from test_cli import generate_and_replay, make_model
+    from test_rumalorn_cpu import plain_for_the_command_line
+
+    folder = make_model(tmp_path, ALL[name], capsys)
+    generate_and_replay(folder, "cuda:0", dtype, capsys, tmp_path, plain_for_the_command_line(folder))

@@ -68,3 +68,12 @@ RUMA_5 = {
     "loop": {"start": 0, "stop": 1, "times": 2},
 }
 ALL["R5"] = RUMA_5
+
+# R6: nothing is a multiple of 4: width 90, heads of 12 (padded to 16), feed-forwards of 30 and 18, vocabulary 101
+_m6 = _mixer(3, 3, 12, 0.3, 9, 0.2, 3, 6)
+RUMA_6 = {
+    "architecture": ARCH, "vocab": 101, "width": 90, "logit_scale": 1.5, "norm": {"eps": 1e-5},
+    "layers": [_layer(_m6, _moe(18, 3, 2)), _layer(_m6, _dense(30, 1.0))],
+    "loop": {"start": 1, "stop": 2, "times": 2},
+}
+ALL["R6"] = RUMA_6

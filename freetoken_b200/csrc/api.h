@@ -63,6 +63,10 @@ typedef struct {
   // multiplied by `scale`; null = none
   const float* dist_bias;
   int dist_len;
+  // more query heads per KV head than a tile has rows: every KV head is taken as kv_split heads of the same keys,
+  // each with 1 / kv_split of its query heads (plan the work list, and size the scratch, for n_kv_heads * kv_split
+  // heads); 0 or 1 = as given.  Not with the tcgen05 kernels.
+  int kv_split;
 } FtkAttnExtras;
 
 const char* ftk_last_error(void);

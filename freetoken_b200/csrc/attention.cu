@@ -55,6 +55,8 @@ struct AttnParams {
   // for query position i and key position j; nullptr: none
   const float* dist_bias;
   int dist_len;
+  // KV heads of the slabs, and how many of this launch's (virtual) KV heads share one of them: Hkv = slab_heads * kv_split
+  int slab_heads, kv_split;
 };
 
 // Bias of a key `dist` positions behind the query, from the row of the query's head (`row` may be null).
@@ -114,7 +116,7 @@ __device__ __forceinline__ long long kv_row_offset(const AttnParams& p, const It
   if (pos < 0) return -1;
   const int page = p.block_table[(size_t)it.bt_row * p.bt_stride + pos / p.P];
   if (page < 0 || page >= p.num_pages) return -1;
-  return (((long long)page * p.Hkv + kvh) * p.P + pos % p.P) * p.D;
+  return (((long long)page * p.slab_heads + kvh / p.kv_split) * p.P + pos % p.P) * p.D;
 }
 
 // ================================================================= float32 path
@@ -996,6 +998,8 @@ static int paged_attention_tc_impl(const void* q, const void* k_slab, const void
   p.sel = nullptr; p.sel_stride = 0; p.block_size = 0; p.arrivals = nullptr;
   p.dist_bias = extras ? extras->dist_bias : nullptr;
   p.dist_len = extras ? extras->dist_len : 0;
+  p.slab_heads = n_kv_heads; p.kv_split = 1;
+  FTK_REQUIRE(!extras || extras->kv_split <= 1, "paged_attention_tc: KV heads are not split for the tcgen05 kernels");
   cudaStream_t s = (cudaStream_t)stream;
   if (p.dist_bias) note_variant(few ? "attention: tcgen05, tiles of at most 16 rows, bias by distance"
                                     : "attention: tcgen05, 128-row query tiles, bias by distance");
@@ -1090,6 +1094,14 @@ static int paged_attention_impl(const void* q, const void* k_slab, const void* v
   p.arrivals = nullptr;
   p.dist_bias = extras ? extras->dist_bias : nullptr;
   p.dist_len = extras ? extras->dist_len : 0;
+  p.slab_heads = n_kv_heads; p.kv_split = 1;
+  if (extras && extras->kv_split > 1) {
+    FTK_REQUIRE(!sel && p.G % extras->kv_split == 0 && (long long)n_kv_heads * extras->kv_split <= 65535,
+                "paged_attention: %d query heads per KV head cannot be split %d ways", p.G, extras->kv_split);
+    p.kv_split = extras->kv_split;
+    p.Hkv = n_kv_heads * p.kv_split;
+    p.G = n_q_heads / p.Hkv;
+  }
   FTK_REQUIRE(!p.dist_bias || p.dist_len >= 1, "paged_attention: a distance bias needs at least one entry per head");
   FTK_REQUIRE(!p.dist_bias || !sel, "paged_attention: a distance bias cannot be combined with block selection");
   if (sel) {
@@ -1099,7 +1111,7 @@ static int paged_attention_impl(const void* q, const void* k_slab, const void* v
                 tile_rows);
   }
   cudaStream_t s = (cudaStream_t)stream;
-  dim3 grid(n_items, n_kv_heads);
+  dim3 grid(n_items, p.Hkv);
   if (dtype == FTK_F32) {
     FTK_REQUIRE(tile_rows == kF32Rows, "paged_attention: the float32 kernel works on %d-row tiles, got %d",
                 kF32Rows, tile_rows);

@@ -74,7 +74,7 @@ class _StreamNorm(ctypes.Structure):
 
 
 class _AttnExtras(ctypes.Structure):
-    _fields_ = [("dist_bias", _vp), ("dist_len", _i)]
+    _fields_ = [("dist_bias", _vp), ("dist_len", _i), ("kv_split", _i)]
 
 
 _SIGNATURES = {
@@ -410,7 +410,7 @@ def paged_attention(q: torch.Tensor, k_slab: torch.Tensor, v_slab: torch.Tensor,
                     items: torch.Tensor, n_items: int, part_o: Optional[torch.Tensor],
                     part_ml: Optional[torch.Tensor], out: torch.Tensor, tile_rows: int, scale: float,
                     window: Optional[int], sel: Optional[torch.Tensor] = None, block_size: int = 0,
-                    few_rows: bool = False, dist_bias: Optional[torch.Tensor] = None) -> None:
+                    few_rows: bool = False, dist_bias: Optional[torch.Tensor] = None, kv_split: int = 1) -> None:
     """Causal softmax attention of the step's queries over the paged keys and values.
 
     ``q, out [T, Hq, D]``; slabs ``[pages, Hkv, page_size, D]``; ``block_table [rows, width]``
@@ -432,6 +432,9 @@ def paged_attention(q: torch.Tensor, k_slab: torch.Tensor, v_slab: torch.Tensor,
     ``dist_bias [Hq, L]`` (float32) adds ``dist_bias[h, min(i - j, L - 1)]`` to the scaled score of query
     position ``i`` and key position ``j`` (a learned bias by distance; not multiplied by ``scale``).
     ``v_slab`` may be ``k_slab`` itself (values that are the keys): each key tile is then brought in once.
+    ``kv_split > 1`` (more query heads per KV head than a tile has rows): every KV head is taken as that many
+    heads of the same keys with a share of its query heads each; the work list and the scratch are then made for
+    ``Hkv * kv_split`` heads.  Not with the tcgen05 kernels.
     Of the tcgen05 kernels the ones with one query tile a piece (128 rows, or at most 16) take the bias; with
     one slab for keys and values their key tile in shared memory serves both products.
     """
@@ -442,8 +445,12 @@ def paged_attention(q: torch.Tensor, k_slab: torch.Tensor, v_slab: torch.Tensor,
     if out.shape != q.shape or out.dtype != q.dtype or k_slab.dtype != q.dtype:
         raise KernelError("paged_attention: dtypes or out shape do not agree")
     n_slots = part_o.shape[0] if part_o is not None else 0
-    if part_o is not None and (part_o.shape[1:] != (Hkv, tile_rows, D) or part_ml is None
-                               or part_ml.shape != (n_slots, Hkv, tile_rows, 2)):
+    kv_split = max(1, int(kv_split))
+    Hv = Hkv * kv_split
+    if kv_split > 1 and ((Hq // Hkv) % kv_split or sel is not None or tile_rows in (128, 256) or few_rows):
+        raise KernelError("paged_attention: kv_split must divide the query heads per KV head (no tcgen05, no selection)")
+    if part_o is not None and (part_o.shape[1:] != (Hv, tile_rows, D) or part_ml is None
+                               or part_ml.shape != (n_slots, Hv, tile_rows, 2)):
         raise KernelError("paged_attention: scratch shapes do not match tile_rows / heads")
     if few_rows and tile_rows != 16:
         raise KernelError(f"paged_attention: few_rows goes with tiles of 16 rows, got {tile_rows}")
@@ -455,7 +462,7 @@ def paged_attention(q: torch.Tensor, k_slab: torch.Tensor, v_slab: torch.Tensor,
             if tile_rows == 256 or dist_bias.dim() != 2 or dist_bias.shape[0] != Hq:
                 raise KernelError("paged_attention: of the tcgen05 kernels the ones with one query tile a piece take a "
                                   "distance bias [Hq, L]")
-            ex = _AttnExtras(_dev(dist_bias, "dist_bias", torch.float32), dist_bias.shape[1])
+            ex = _AttnExtras(_dev(dist_bias, "dist_bias", torch.float32), dist_bias.shape[1], 1)
             _check(_lib().ftk_paged_attention_tc_ex(
                 _dev(q, "q"), _dev(k_slab, "k_slab"), _dev(v_slab, "v_slab"),
                 _dev(block_table, "block_table", torch.int32), block_table.shape[1],
@@ -490,10 +497,11 @@ def paged_attention(q: torch.Tensor, k_slab: torch.Tensor, v_slab: torch.Tensor,
             _dev(sel, "sel", torch.int32), sel.shape[2], int(block_size), _stream()),
             "paged_attention (block-sparse)", 2 if n_slots else 1)
         return
-    if dist_bias is not None:
-        if dist_bias.dim() != 2 or dist_bias.shape[0] != Hq or dist_bias.shape[1] < 1:
+    if dist_bias is not None or kv_split > 1:
+        if dist_bias is not None and (dist_bias.dim() != 2 or dist_bias.shape[0] != Hq or dist_bias.shape[1] < 1):
             raise KernelError("paged_attention: dist_bias must be [Hq, L]")
-        ex = _AttnExtras(_dev(dist_bias, "dist_bias", torch.float32), dist_bias.shape[1])
+        ex = _AttnExtras(_dev(dist_bias, "dist_bias", torch.float32), dist_bias.shape[1] if dist_bias is not None else 0,
+                         kv_split)
         _check(_lib().ftk_paged_attention_ex(
             _dev(q, "q"), _dev(k_slab, "k_slab"), _dev(v_slab, "v_slab"), _code(q, "q"),
             _dev(block_table, "block_table", torch.int32), block_table.shape[1],

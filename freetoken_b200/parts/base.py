@@ -116,17 +116,20 @@ class Workspace:
 
     A buffer is allocated at its first request with the largest size any step can ask
     for and handed out as a view afterwards, so steps allocate nothing and CUDA graphs
-    see fixed addresses."""
+    see fixed addresses.  A buffer is known by its name *and its row shape*: layers of different
+    sizes that ask under one name (a model whose layers differ in heads, widths or expert counts) get
+    a buffer each, so none of them can outgrow a buffer that a recorded graph still points to."""
 
     def __init__(self, device: torch.device):
         self.device = device
-        self._buffers: Dict[str, torch.Tensor] = {}
+        self._buffers: Dict[Any, torch.Tensor] = {}
 
     def get(self, name: str, shape: Tuple[int, ...], dtype: torch.dtype,
             max_shape: Optional[Tuple[int, ...]] = None) -> torch.Tensor:
         n = 1
         for s in shape:
             n *= s
+        name = (name, tuple(int(x) for x in shape[1:]))
         buf = self._buffers.get(name)
         if buf is None or buf.dtype != dtype or buf.numel() < n:
             cap = n

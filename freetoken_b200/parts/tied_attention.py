@@ -91,9 +91,13 @@ class TiedKVAttention(Mixer):
         self.position = shared_position(pos, env) if pos is not None else None
         if self.position is not None and not hasattr(self.position, "scale_table"):
             raise ConfigError("tied_kv_attention: the position encoding must give a factor per position")
+        # more query heads per KV head than the kernels' tiles have rows: every KV head is taken as `kv_split` heads of
+        # the same keys (the smallest split that fits), and the work is planned for that many heads
         rows, _ = attention_kernel_form(env.dtype)
-        if self.group > (rows if env.dtype != torch.bfloat16 else 64):
-            raise ConfigError(f"tied_kv_attention: {self.group} query heads per KV head exceed the kernel's tile")
+        most = rows if env.dtype != torch.bfloat16 else 64
+        self.kv_split = next(s for s in range(1, self.group + 1) if self.group % s == 0 and self.group // s <= most)
+        self.plan_group = self.group // self.kv_split
+        self.plan_kv_heads = self.n_kv_heads * self.kv_split
         self.q_dim = self.n_heads * self.head_dim
         self.kv_dim = self.n_kv_heads * self.head_dim
         self.proj_rows = self.q_dim + self.kv_dim + (self.n_heads if self.gate else 0)
@@ -140,18 +144,20 @@ class TiedKVAttention(Mixer):
     # ------------------------------------------------------------------ step
     def kernel_form(self, decode_only: bool, n_tokens: int = 0, page_size: int = 0, longest_span: int = 0):
         # (of the tcgen05 kernels the ones with a single query tile a piece take a bias by distance)
-        return attention_kernel_form(self.env.dtype, decode_only, self.group, n_tokens, self.pad_dim, page_size,
-                                     self.window, longest_span, one_tile_only=True)
+        return attention_kernel_form(self.env.dtype, decode_only, self.plan_group, n_tokens,
+                                     self.pad_dim if self.kv_split == 1 else 0, page_size, self.window, longest_span,
+                                     one_tile_only=True)
 
     def plan_key(self, decode_only: bool = False, n_tokens: int = 0, page_size: int = 0, longest_span: int = 0):
         rows, few_rows = self.kernel_form(decode_only, n_tokens, page_size, longest_span)
-        return ("attention", self.group, rows, self.window, self.n_kv_heads, self.pad_dim, few_rows)
+        return ("attention", self.plan_group, rows, self.window, self.plan_kv_heads, self.pad_dim, few_rows)
 
     def prepare(self, builder) -> None:
         n_tokens = sum(q for q, _ in builder.seg_lens)
         page_size = builder.engine.config.page_size if builder.engine is not None else 0
         rows, few_rows = self.kernel_form(builder.decode_only, n_tokens, page_size, builder.longest_span())
-        self._step_plan = builder.attention_plan(self.group, rows, self.window, self.n_kv_heads, self.pad_dim, few_rows)
+        self._step_plan = builder.attention_plan(self.plan_group, rows, self.window, self.plan_kv_heads, self.pad_dim,
+                                                 few_rows)
 
     def forward(self, h: torch.Tensor, step: StepState, cache: Any, writes_cache: bool) -> torch.Tensor:
         T = h.shape[0]
@@ -173,7 +179,7 @@ class TiedKVAttention(Mixer):
         k = cache.slabs["k"]
         ops.paged_attention(q, k, k, cache.block_table, step.seg_info, len(step.segments), plan.items_dev,
                             plan.n_items, plan.part_o, plan.part_ml, o, self._step_plan[2], self.scale, self.window,
-                            few_rows=self._step_plan[6], dist_bias=self._dist_bias)
+                            few_rows=self._step_plan[6], dist_bias=self._dist_bias, kv_split=self.kv_split)
         if self.gate:
             ops.head_gate(o, qkg[:, self.q_dim + self.kv_dim:])
         out = ws.get("tied.out", (T, self.hidden), dt, (cap, self.hidden))

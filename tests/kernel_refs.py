@@ -111,7 +111,7 @@ def norm_rope_store(x, head_dim, rotary_dim, positions, rope_table, eps, gemma, 
 
 
 def paged_attention(q, k_slab, v_slab, block_table, seg_info, n_segs, items, n_items, part_o, part_ml,
-                    out, tile_rows, scale, window, sel=None, block_size=0, few_rows=False, dist_bias=None):
+                    out, tile_rows, scale, window, sel=None, block_size=0, few_rows=False, dist_bias=None, kv_split=1):
     """Per query token, softmax over the visible keys gathered through the block table; the
     work list and the scratch are ignored (they only steer how the kernel splits the work).
     With ``sel`` a query reads only the keys of its chosen blocks."""

@@ -24,7 +24,7 @@ from freetoken_b200.config.spec import PartSpec
 from freetoken_b200.registry import architecture_of
 
 TOL = dict(rtol=1e-4, atol=2e-5)
-PAGE = {"R1": 4, "R2": 8, "R3": 4, "R4": 16, "R6": 8}
+PAGE = {"R1": 4, "R2": 8, "R3": 4, "R4": 16, "R6": 8, "R7": 4}
 
 
 @pytest.fixture
@@ -122,7 +122,7 @@ def test_names_shapes_and_table_rows_from_the_file(tmp_path_factory):
 
 
 # --------------------------------------------------------------------------- the engine on the CPU
-@pytest.mark.parametrize("name", ["R1", "R2", "R3", "R4", "R6"])
+@pytest.mark.parametrize("name", ["R1", "R2", "R3", "R4", "R6", "R7"])
 def test_cuts_and_batches_agree_with_the_plain_model(name, cpu_ops, tmp_path_factory):
     folder = model_folder(tmp_path_factory.getbasetemp(), name, ALL[name])
     plain = PlainRumalorn(folder)

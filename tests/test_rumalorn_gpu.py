@@ -18,7 +18,7 @@ from freetoken_b200.kernels import ops
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 DTYPES = [torch.float32, torch.bfloat16]
-PAGE = {"R1": 4, "R2": 8, "R3": 4, "R4": 16, "R5": 16, "R6": 8}
+PAGE = {"R1": 4, "R2": 8, "R3": 4, "R4": 16, "R5": 16, "R6": 8, "R7": 4}
 
 
 def rnd(*shape, dtype=torch.float32, scale=1.0, seed=0):
@@ -150,23 +150,24 @@ def attention_problem(dtype, Hq, Hkv, D, P, segs, seed=0, scale_k=1.0):
 
 
 def run_biased(dtype, Hq, Hkv, D, P, segs, dist_bias, tile, fixed_splits=None, force_split=False, q=None, problem=None,
-               few_rows=False):
+               few_rows=False, kv_split=1):
     qq, ks, bt, seg = problem or attention_problem(dtype, Hq, Hkv, D, P, segs)
     q = qq if q is None else q
     kw = dict(sm_count=4096, min_split_keys=32) if force_split else dict(sm_count=148)
     if tile == 128 or few_rows:
         kw["key_tile"] = 128  # as the engine plans the tcgen05 kernels' work
-    plan = build_plan(segs, Hq // Hkv, tile, None, Hkv, fixed_splits=fixed_splits, **kw)
+    Hv = Hkv * kv_split  # the kernel takes every KV head as kv_split heads of the same keys
+    plan = build_plan(segs, Hq // Hv, tile, None, Hv, fixed_splits=fixed_splits, **kw)
     items = torch.from_numpy(plan.items).to(DEV)
     part_o = part_ml = None
     if plan.n_slots:
-        part_o = torch.full((plan.n_slots, Hkv, tile, D), float("nan"), dtype=torch.float32, device=DEV)
-        part_ml = torch.full((plan.n_slots, Hkv, tile, 2), float("nan"), dtype=torch.float32, device=DEV)
+        part_o = torch.full((plan.n_slots, Hv, tile, D), float("nan"), dtype=torch.float32, device=DEV)
+        part_ml = torch.full((plan.n_slots, Hv, tile, 2), float("nan"), dtype=torch.float32, device=DEV)
     out = torch.full(q.shape, float("nan"), dtype=dtype, device=DEV)
     want = torch.empty_like(out)
     scale = 0.8 * D ** -0.5
     ops.paged_attention(q, ks, ks, bt, seg, len(segs), items, plan.n_items, part_o, part_ml, out, tile, scale, None,
-                        dist_bias=dist_bias, few_rows=few_rows)
+                        dist_bias=dist_bias, few_rows=few_rows, kv_split=kv_split)
     ref.paged_attention(q, ks, ks, bt, seg, len(segs), items, plan.n_items, None, None, want, tile, scale, None,
                         dist_bias=dist_bias)
     return out, want, plan
@@ -192,6 +193,19 @@ def test_attention_with_distance_bias_and_keys_as_values(dtype, Hq, Hkv, D, P, L
     out, want, plan = run_biased(dtype, Hq, Hkv, D, P, segs, bias, tile, force_split=True)
     assert plan.n_slots > 0
     torch.testing.assert_close(out.float(), want.float(), **attn_tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("Hq,Hkv,D,split", [(40, 1, 16, 4), (48, 2, 32, 2), (160, 2, 16, 5)])
+def test_more_query_heads_per_kv_head_than_a_tile_has_rows(dtype, Hq, Hkv, D, split):
+    bias = rnd(Hq, 9, seed=3)
+    tile = 64 if dtype == torch.bfloat16 else 16
+    for segs, t, fixed, force in (([(1, 1), (30, 30), (2, 131), (33, 97)], tile, None, False), ([(1, 300), (1, 17)], 16, 3, False),
+                                  ([(20, 400)], tile, None, True)):
+        if t == 16 and dtype == torch.bfloat16 and Hq // Hkv // split > 16:
+            t = 64
+        out, want, plan = run_biased(dtype, Hq, Hkv, D, 8, segs, bias, t, fixed_splits=fixed, force_split=force, kv_split=split)
+        torch.testing.assert_close(out.float(), want.float(), **attn_tol(dtype))
 
 
 @pytest.mark.parametrize("Hq,Hkv,P,L", [(12, 2, 16, 200), (4, 4, 32, 7), (16, 1, 16, 130), (6, 2, 64, 1)])
@@ -276,7 +290,7 @@ def test_a_far_key_that_matches_the_query_stands_out(dtype):
 
 # --------------------------------------------------------------------------- the engine against the plain model
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["R1", "R2", "R3", "R4", "R5", "R6"])
+@pytest.mark.parametrize("name", ["R1", "R2", "R3", "R4", "R5", "R6", "R7"])
 def test_cuts_and_batches_agree_with_the_plain_model(name, dtype, tmp_path_factory):
     folder = model_folder(tmp_path_factory.getbasetemp(), name, ALL[name])
     plain = PlainRumalorn(folder)

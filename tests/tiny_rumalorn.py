@@ -77,3 +77,11 @@ RUMA_6 = {
     "loop": {"start": 1, "stop": 2, "times": 2},
 }
 ALL["R6"] = RUMA_6
+
+# R7: 80 query heads on one KV head (more than any attention tile has rows: the KV head is split), heads of 8
+_m7 = _mixer(80, 1, 8, 0.35, 15, 0.25, 5, 8)
+RUMA_7 = {
+    "architecture": ARCH, "vocab": 90, "width": 48, "logit_scale": 1.0, "norm": {"eps": 1e-5},
+    "layers": [_layer(_m7, _dense(32, 2.0)), _layer(_m7, None)],
+}
+ALL["R7"] = RUMA_7

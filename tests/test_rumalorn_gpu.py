@@ -360,6 +360,25 @@ def test_long_steps_of_heads_of_128_run_the_tensor_core_attention(tmp_path_facto
     eng.check_kernels()
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_long_step_after_recorded_decode_steps_of_layers_that_differ_in_size(dtype, tmp_path_factory):
+    """Decode steps are replayed from CUDA graphs that hold the addresses of the work buffers; a later step that
+    is long enough to need the larger of two layers' buffers must not move what the graphs point to."""
+    folder = model_folder(tmp_path_factory.getbasetemp(), "R4", ALL["R4"])
+    plain = PlainRumalorn(folder)
+    a, b = tokens_for(plain.vocab, 40, 1), tokens_for(plain.vocab, 230, 2)
+    eng = make_engine(folder, dtype, DEV, 16, pages=40, max_step=256)
+    got = [eng.step([StepEntry("a", a[:3], [0, 1, 2])]).logits.float().cpu().clone()]
+    for i in range(3, 12):  # recorded at the first of these, replayed afterwards
+        got.append(eng.step([StepEntry("a", a[i:i + 1], [0])]).logits.float().cpu().clone())
+    long = eng.step([StepEntry("b", b, list(range(len(b))))]).logits.float().cpu().clone()
+    for i in range(12, 40):
+        got.append(eng.step([StepEntry("a", a[i:i + 1], [0])]).logits.float().cpu().clone())
+    assert_rows(long, plain.logits(b), dtype, "the long step")
+    assert_rows(torch.cat(got), plain.logits(a), dtype, "decode steps before and after it")
+    assert eng.graphs, "the decode steps were meant to be replayed from graphs"
+
+
 def test_greedy_generation_through_the_scheduler(tmp_path_factory):
     from freetoken_b200 import LLM, SamplingParams
 

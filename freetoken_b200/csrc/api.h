@@ -10,6 +10,10 @@
 #define FTK_ACT_SWIGLUOAI 1
 #define FTK_SCORE_SIGMOID 0
 #define FTK_SCORE_SOFTMAX 1
+#define FTK_GATE_SIGMOID 0
+#define FTK_GATE_SILU 1
+// the bias belongs to the logit: choice by logit + bias, weights = softmax of logit + bias over the chosen experts
+#define FTK_SCORE_SOFTMAX_OF_CHOSEN 2
 
 #ifdef __cplusplus
 extern "C" {
@@ -67,6 +71,10 @@ typedef struct {
   // each with 1 / kv_split of its query heads (plan the work list, and size the scratch, for n_kv_heads * kv_split
   // heads); 0 or 1 = as given.  Not with the tcgen05 kernels.
   int kv_split;
+  // a sink in the softmax's denominator: weight_j = e^(s_j) / (e^sink_logit + sum_i e^(s_i)); the sink has no value.
+  // Not with the tcgen05 kernels, nor with block selection.
+  int has_sink;
+  float sink_logit;
 } FtkAttnExtras;
 
 const char* ftk_last_error(void);
@@ -90,6 +98,34 @@ int ftk_head_gate(void* o, int dtype, const void* gates, long long gate_stride, 
 int ftk_table_route(const int32_t* token_ids, const int32_t* table, int n_tokens, int vocab, int top_k,
                     int n_experts, float weight, int32_t* ids, float* weights, void* stream);
 int ftk_scale_f32(float* x, long long n, float s, void* stream);
+// x <- cap * tanh(x / cap)
+int ftk_softcap_f32(float* x, long long n, float cap, void* stream);
+// A sub-layer's output joins the stream through a norm of its own, and the stream is normed for the next
+// sub-layer in the same pass: residual += rms(a) w_post; out = rms(residual) w_pre (w = 1 + weight with gemma).
+// a = x[row] or, with route_pos, sum_j x[route_pos[row * top_k + j]] (+ shared[row]) in 32 bits.  Without pre_w
+// only the stream is updated; with `rows` only those rows are normed and the stream is left as it is.
+int ftk_postnorm_add_norm(const void* x, int dtype, const int32_t* route_pos, int top_k, int n_routes,
+                          const void* shared, const float* post_w, float post_eps, int post_gemma, float* residual,
+                          const float* pre_w, float pre_eps, int pre_gemma, void* out, float* out_f32,
+                          const int32_t* rows, int n_rows, int hidden, void* stream);
+// out[t, h, :dim] = norm(x[t, h, :dim]) * act(gates[t * gate_stride + h * dim + :]); the RMS norm over the head
+// (plain weight norm_w [dim]) is left out when norm_w is null; act: FTK_GATE_SIGMOID | FTK_GATE_SILU.  x is
+// float32 (x_f32) or of `dtype`, rows x_stride apart; out is of `dtype`, rows out_stride apart, and may be x.
+int ftk_gated_heads(const void* x, int x_f32, int x_stride, const void* gates, long long gate_stride,
+                    const float* norm_w, float eps, int act, void* out, int out_stride, int dtype, int n_tokens,
+                    int n_heads, int dim, void* stream);
+// Gated linear attention over a step's tokens (recurrent.cu): per (request, head) S <- diag(a_t) S + k_t v_t^T,
+// o_t = S^T (q_t q_scale), a_t = sigmoid(z_t + z_bias)^(1 / tau); state [n_slots, H, dim, vdim] float32, zero for
+// requests whose first tokens these are (kv_len == q_len in seg_info).  chunks [n_chunks, 4] = segment, first token
+// within the segment, tokens, place among the segment's chunks (consecutive per segment); seg_chunks [n_segs, 2] =
+// first chunk, chunks.  carry [n_chunks, H, dim, vdim] and decay_prod [n_chunks, H, dim] are scratch for segments
+// of several chunks.  out [T, H, vdim] float32.
+int ftk_gla_scan(const void* q, long long q_stride, const void* k, long long k_stride, const void* v,
+                 long long v_stride, int dtype, const float* z, const float* z_bias, float tau, float q_scale,
+                 float* state, int n_slots, const int32_t* state_slots, const int32_t* seg_info, int n_segs,
+                 const int32_t* chunks, int n_chunks, const int32_t* seg_chunks, int any_single, int any_multi,
+                 float* carry, float* decay_prod, float* out, int n_tokens, int n_heads, int dim, int vdim,
+                 void* stream);
 int ftk_act_and_mul(const void* gate_up, int dtype, int n_rows, int inter, int act, float alpha,
                     float limit, void* out, void* stream);
 int ftk_cast(const void* src, int src_dtype, void* dst, int dst_dtype, long long n, void* stream);

@@ -57,7 +57,16 @@ struct AttnParams {
   int dist_len;
   // KV heads of the slabs, and how many of this launch's (virtual) KV heads share one of them: Hkv = slab_heads * kv_split
   int slab_heads, kv_split;
+  // a sink in the softmax's denominator: p_j = e^(s_j) / (e^sink + sum_i e^(s_i)); it has no value, so a row's
+  // weights add up to less than one.  Added once per row, where the row is normalised (a split tile: in the merge).
+  int has_sink;
+  float sink;
 };
+
+// What the sink adds to a row's sum of exponentials taken relative to the maximum `m` (natural logarithm domain).
+__device__ __forceinline__ float sink_term(const AttnParams& p, float m) {
+  return p.has_sink ? expf(p.sink - m) : 0.f;
+}
 
 // Bias of a key `dist` positions behind the query, from the row of the query's head (`row` may be null).
 __device__ __forceinline__ float dist_bias_at(const float* row, int dist_len, int dist) {
@@ -214,7 +223,8 @@ __global__ void __launch_bounds__(kF32Rows * 32) attention_f32_kernel(AttnParams
   const int tok = it.q_start + it.tok0 + warp / G;
   if (it.nsplit == 1) {
     T* o = (T*)p.out + ((size_t)tok * p.Hq + kvh * G + warp % G) * D;
-    const float inv = l > 0.f ? 1.f / l : 0.f;
+    const float lt = l + sink_term(p, m);
+    const float inv = lt > 0.f ? 1.f / lt : 0.f;
 #pragma unroll
     for (int i = 0; i < kPer; ++i) {
       const int d = lane + 32 * i;
@@ -289,7 +299,7 @@ __global__ void __launch_bounds__(512) attention_merge_kernel(AttnParams p) {
       wgt[j] = w;
       L += lsum[j] * w;
     }
-    L = warp_sum(L);
+    L = warp_sum(L) + sink_term(p, M);
     const float inv = L > 0.f ? 1.f / L : 0.f;
     const int tok = it.q_start + it.tok0 + r / G;
     T* o = (T*)p.out + ((size_t)tok * p.Hq + kvh * G + r % G) * D;
@@ -571,7 +581,10 @@ __global__ void __launch_bounds__(128) attention_bf16_kernel(AttnParams p) {
   // epilogue
   if (it.nsplit == 1) {
     __nv_bfloat16* out = (__nv_bfloat16*)p.out;
-    const float i0 = l0 > 0.f ? 1.f / l0 : 0.f, i1 = l1 > 0.f ? 1.f / l1 : 0.f;
+    // (the running maxima are in the exp2 domain)
+    const float ln2e = 0.6931471805599453f;
+    const float t0 = l0 + sink_term(p, m0 * ln2e), t1 = l1 + sink_term(p, m1 * ln2e);
+    const float i0 = t0 > 0.f ? 1.f / t0 : 0.f, i1 = t1 > 0.f ? 1.f / t1 : 0.f;
     if (r0 < R) {
       __nv_bfloat16* dst = out + ((size_t)(it.q_start + it.tok0 + r0 / G) * p.Hq + kvh * G + r0 % G) * D;
 #pragma unroll
@@ -641,6 +654,7 @@ __device__ __forceinline__ void merge_tile_rows_bf16(const AttnParams& p, const 
       L += sl[r * S + sp] * w;
       sm[r * S + sp] = w;
     }
+    L += sink_term(p, M);
     sinv[r] = L > 0.f ? 1.f / L : 0.f;
   }
   __syncthreads();
@@ -874,7 +888,8 @@ __global__ void __launch_bounds__(128) attention_decode_bf16_kernel(AttnParams p
     const int tok = it.q_start + it.tok0 + r / G;
     if (it.nsplit == 1) {
       __nv_bfloat16* out = (__nv_bfloat16*)p.out + ((size_t)tok * p.Hq + kvh * G + r % G) * D;
-      out[d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+      const float Lt = L + sink_term(p, M * ln2);
+      out[d] = __float2bfloat16_rn(Lt > 0.f ? acc / Lt : 0.f);
     } else {
       const size_t slot = ((size_t)(it.base + it.split) * p.Hkv + kvh) * p.tile_rows + r;
       p.part_o[slot * D + d] = acc;
@@ -1000,6 +1015,8 @@ static int paged_attention_tc_impl(const void* q, const void* k_slab, const void
   p.dist_len = extras ? extras->dist_len : 0;
   p.slab_heads = n_kv_heads; p.kv_split = 1;
   FTK_REQUIRE(!extras || extras->kv_split <= 1, "paged_attention_tc: KV heads are not split for the tcgen05 kernels");
+  p.has_sink = 0; p.sink = 0.f;
+  FTK_REQUIRE(!extras || !extras->has_sink, "paged_attention_tc: a softmax sink runs on the other kernels");
   cudaStream_t s = (cudaStream_t)stream;
   if (p.dist_bias) note_variant(few ? "attention: tcgen05, tiles of at most 16 rows, bias by distance"
                                     : "attention: tcgen05, 128-row query tiles, bias by distance");
@@ -1095,6 +1112,9 @@ static int paged_attention_impl(const void* q, const void* k_slab, const void* v
   p.dist_bias = extras ? extras->dist_bias : nullptr;
   p.dist_len = extras ? extras->dist_len : 0;
   p.slab_heads = n_kv_heads; p.kv_split = 1;
+  p.has_sink = extras ? extras->has_sink : 0;
+  p.sink = extras ? extras->sink_logit : 0.f;
+  FTK_REQUIRE(!p.has_sink || !sel, "paged_attention: a sink cannot be combined with block selection");
   if (extras && extras->kv_split > 1) {
     FTK_REQUIRE(!sel && p.G % extras->kv_split == 0 && (long long)n_kv_heads * extras->kv_split <= 65535,
                 "paged_attention: %d query heads per KV head cannot be split %d ways", p.G, extras->kv_split);

@@ -1,0 +1,270 @@
+// Gated linear attention: a matrix state per (request, head), S <- diag(a_t) S + k_t v_t^T, o_t = S^T q_t,
+// with a decay a_t = sigmoid(z_t)^(1 / tau) per key channel.  State, decays and all sums are 32-bit.
+//
+// A step's tokens are cut into chunks of at most `chunk` consecutive tokens of one request (the host
+// lists them: 4 int32 per chunk = segment, first token within the segment's tokens, tokens, place of
+// the chunk among the segment's chunks; and per segment: first chunk, chunks).  A request with one
+// chunk (every decode step) takes one launch: the recurrence runs from the request's state slot and
+// leaves the new state there.  Longer portions take three launches, so that chunks run side by side:
+//   1. every chunk but a segment's last runs the recurrence from a zero state: its own contribution
+//      L_c = sum_s (prod_{r > s} a_r) k_s v_s^T, and the product of its decays P_c;
+//   2. per segment and state element, one after the other: S_(c+1) = P_c S_c + L_c, with S_0 the slot's
+//      state (zero for a request's first tokens); S_(c+1) overwrites L_c, and S_0 goes where the last chunk's
+//      L would lie, so that step 3 never reads a slot that its last chunk is writing;
+//   3. every chunk runs the recurrence from its start state and writes its tokens' outputs; a
+//      segment's last chunk leaves the final state in the slot.
+// The recurrence itself is the plain one, token by token, so the result differs from a pure scan only
+// by the rounding of step 2's sums.
+//
+// A block owns 32 value columns of one (chunk, head): 4 warps split the key channels, a thread keeps
+// its share of one state column in registers, and the tokens' q, k and decays are staged in shared
+// memory 32 tokens at a time (float4 reads, the same address for the whole warp).
+#include "common.cuh"
+
+namespace ftk {
+
+constexpr int kGlaCols = 32;     // value columns per block
+constexpr int kGlaSlices = 4;    // warps per block: each takes a quarter of the key channels
+constexpr int kGlaBatch = 32;    // tokens staged at a time
+
+struct GlaArgs {
+  const void* q; const void* k; const void* v;  // rows of the engine's type: token t at + t * stride, head h at + h * dim
+  long long q_stride, k_stride, v_stride;
+  const float* z;          // [T, H * D] decay logits (before the bias)
+  const float* z_bias;     // [H * D] or null
+  float inv_tau, q_scale;
+  float* state;            // [slots, H, D, Dv]
+  const int32_t* state_slots;  // [S]
+  const int32_t* seg_info;     // [S, 4]: q_start, q_len, kv_len, -
+  const int32_t* chunks;       // [n_chunks, 4]
+  const int32_t* seg_chunks;   // [S, 2]: first chunk, chunks
+  int n_chunks, n_segs, n_slots;
+  float* carry;            // [n_chunks, H, D, Dv]: L_c, then the start state of chunk c + 1
+  float* decay_prod;       // [n_chunks, H, D]
+  float* out;              // [T, H, Dv]
+  int H, D, Dv, n_tokens;
+};
+
+__device__ __forceinline__ float decay_of(float z, float inv_tau) {
+  // sigmoid(z)^(1 / tau) = exp(-softplus(-z) / tau)
+  const float sp = z > 0.f ? log1pf(expf(-z)) : -z + log1pf(expf(z));
+  return expf(-sp * inv_tau);
+}
+
+// MODE 0: one launch for segments of one chunk (state slot -> outputs -> state slot)
+// MODE 1: local contribution of a chunk from a zero state (no outputs)
+// MODE 3: outputs of a chunk from its start state
+template <typename T, int DPT, int MODE>
+__global__ void __launch_bounds__(kGlaSlices * 32) gla_chunk_kernel(GlaArgs a) {
+  pdl_wait();
+  pdl_trigger();
+  extern __shared__ float sm[];
+  const int D = a.D, Dv = a.Dv;
+  const int Dp = DPT * kGlaSlices;              // padded key channels
+  float* sq = sm;                               // [batch][Dp]
+  float* sk = sq + kGlaBatch * Dp;
+  float* sa = sk + kGlaBatch * Dp;
+  float* sv = sa + kGlaBatch * Dp;              // [batch][cols]
+  float* part = sv + kGlaBatch * kGlaCols;      // [slices][batch][cols]
+  const int c = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * kGlaCols;
+  const int32_t* ch = a.chunks + (size_t)c * 4;
+  const int seg = ch[0], tok0 = ch[1], ntok = ch[2], place = ch[3];
+  if (seg < 0 || seg >= a.n_segs || ntok <= 0) return;
+  const int q_start = a.seg_info[seg * 4], q_len = a.seg_info[seg * 4 + 1], kv_len = a.seg_info[seg * 4 + 2];
+  const int n_seg_chunks = a.seg_chunks[seg * 2 + 1];
+  if (tok0 < 0 || tok0 + ntok > q_len || q_start < 0 || q_start + q_len > a.n_tokens) return;
+  const bool single = n_seg_chunks == 1, last = place == n_seg_chunks - 1;
+  if (MODE == 0 && !single) return;
+  if (MODE == 1 && (single || last)) return;
+  if (MODE == 3 && single) return;
+  const int slot = a.state_slots[seg];
+  if (slot < 0 || slot >= a.n_slots) return;
+  const int slice = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int col = col0 + lane;
+  const bool col_ok = col < Dv;
+  const int d0 = slice * DPT;
+  float s[DPT];
+  // the start state
+  const bool fresh = kv_len - q_len == 0;
+  const float* src = nullptr;
+  if (MODE == 0) {
+    if (!fresh) src = a.state + ((size_t)slot * a.H + h) * D * Dv;
+  } else if (MODE == 3) {  // chunk 0 finds its start state in the last chunk's place, the others in the chunk's before
+    const int from = place == 0 ? c + n_seg_chunks - 1 : c - 1;
+    src = a.carry + ((size_t)from * a.H + h) * D * Dv;
+  }
+#pragma unroll
+  for (int i = 0; i < DPT; ++i) s[i] = (src && col_ok && d0 + i < D) ? src[(size_t)(d0 + i) * Dv + col] : 0.f;
+  float pa[DPT];  // MODE 1: the product of the chunk's decays (the lanes of a warp hold the same values)
+  if (MODE == 1) {
+#pragma unroll
+    for (int i = 0; i < DPT; ++i) pa[i] = 1.f;
+  }
+  const T* qb = (const T*)a.q;
+  const T* kb = (const T*)a.k;
+  const T* vb = (const T*)a.v;
+  for (int b0 = 0; b0 < ntok; b0 += kGlaBatch) {
+    const int nb = min(kGlaBatch, ntok - b0);
+    __syncthreads();
+    for (int i = threadIdx.x; i < nb * Dp; i += blockDim.x) {
+      const int t = i / Dp, d = i % Dp;
+      const size_t tok = (size_t)(q_start + tok0 + b0 + t);
+      float qv = 0.f, kv = 0.f, av = 1.f;
+      if (d < D) {
+        if (MODE != 1) qv = to_float(qb[tok * a.q_stride + (size_t)h * D + d]) * a.q_scale;
+        kv = to_float(kb[tok * a.k_stride + (size_t)h * D + d]);
+        const float z = a.z[(tok * a.H + h) * D + d] + (a.z_bias ? a.z_bias[(size_t)h * D + d] : 0.f);
+        av = decay_of(z, a.inv_tau);
+      }
+      sq[i] = qv; sk[i] = kv; sa[i] = av;
+    }
+    for (int i = threadIdx.x; i < nb * kGlaCols; i += blockDim.x) {
+      const int t = i / kGlaCols, j = i % kGlaCols;
+      const size_t tok = (size_t)(q_start + tok0 + b0 + t);
+      sv[i] = col0 + j < Dv ? to_float(vb[tok * a.v_stride + (size_t)h * Dv + col0 + j]) : 0.f;
+    }
+    __syncthreads();
+    for (int t = 0; t < nb; ++t) {
+      const float vj = sv[t * kGlaCols + lane];
+      const float4* q4 = reinterpret_cast<const float4*>(sq + t * Dp + d0);
+      const float4* k4 = reinterpret_cast<const float4*>(sk + t * Dp + d0);
+      const float4* a4 = reinterpret_cast<const float4*>(sa + t * Dp + d0);
+      float acc = 0.f;
+#pragma unroll
+      for (int i = 0; i < DPT / 4; ++i) {
+        const float4 av = a4[i], kv = k4[i];
+        s[4 * i + 0] = fmaf(av.x, s[4 * i + 0], kv.x * vj);
+        s[4 * i + 1] = fmaf(av.y, s[4 * i + 1], kv.y * vj);
+        s[4 * i + 2] = fmaf(av.z, s[4 * i + 2], kv.z * vj);
+        s[4 * i + 3] = fmaf(av.w, s[4 * i + 3], kv.w * vj);
+        if (MODE == 1) {
+          pa[4 * i + 0] *= av.x; pa[4 * i + 1] *= av.y; pa[4 * i + 2] *= av.z; pa[4 * i + 3] *= av.w;
+        } else {
+          const float4 qv = q4[i];
+          acc = fmaf(s[4 * i + 0], qv.x, acc);
+          acc = fmaf(s[4 * i + 1], qv.y, acc);
+          acc = fmaf(s[4 * i + 2], qv.z, acc);
+          acc = fmaf(s[4 * i + 3], qv.w, acc);
+        }
+      }
+      if (MODE != 1) part[(slice * kGlaBatch + t) * kGlaCols + lane] = acc;
+    }
+    if (MODE != 1) {
+      __syncthreads();
+      for (int i = threadIdx.x; i < nb * kGlaCols; i += blockDim.x) {
+        const int t = i / kGlaCols, j = i % kGlaCols;
+        if (col0 + j < Dv) {
+          float o = 0.f;
+#pragma unroll
+          for (int w = 0; w < kGlaSlices; ++w) o += part[(w * kGlaBatch + t) * kGlaCols + j];  // slices in order
+          a.out[((size_t)(q_start + tok0 + b0 + t) * a.H + h) * Dv + col0 + j] = o;
+        }
+      }
+    }
+  }
+  // where the state goes
+  float* dst = nullptr;
+  if (MODE == 0 || (MODE == 3 && last)) dst = a.state + ((size_t)slot * a.H + h) * D * Dv;
+  if (MODE == 1) dst = a.carry + ((size_t)c * a.H + h) * D * Dv;
+  if (dst && col_ok) {
+#pragma unroll
+    for (int i = 0; i < DPT; ++i)
+      if (d0 + i < D) dst[(size_t)(d0 + i) * Dv + col] = s[i];
+  }
+  if (MODE == 1 && blockIdx.z == 0 && lane == 0) {
+#pragma unroll
+    for (int i = 0; i < DPT; ++i)
+      if (d0 + i < D) a.decay_prod[((size_t)c * a.H + h) * D + d0 + i] = pa[i];
+  }
+}
+
+// Step 2: a thread per state element of a (segment, head) walks the segment's chunks.
+__global__ void gla_carry_kernel(GlaArgs a) {
+  pdl_wait();
+  pdl_trigger();
+  const int seg = blockIdx.y, h = blockIdx.z;
+  const int first = a.seg_chunks[seg * 2], n = a.seg_chunks[seg * 2 + 1];
+  if (n <= 1 || first < 0 || first + n > a.n_chunks) return;
+  const int slot = a.state_slots[seg];
+  if (slot < 0 || slot >= a.n_slots) return;
+  const size_t DV = (size_t)a.D * a.Dv;
+  const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= DV) return;
+  const int d = (int)(e / a.Dv);
+  const bool fresh = a.seg_info[seg * 4 + 2] - a.seg_info[seg * 4 + 1] == 0;
+  float s = fresh ? 0.f : a.state[((size_t)slot * a.H + h) * DV + e];
+  a.carry[((size_t)(first + n - 1) * a.H + h) * DV + e] = s;
+  for (int c = first; c < first + n - 1; ++c) {
+    float* l = a.carry + ((size_t)c * a.H + h) * DV + e;
+    s = fmaf(a.decay_prod[((size_t)c * a.H + h) * a.D + d], s, *l);
+    *l = s;
+  }
+}
+
+template <typename T, int DPT>
+static int launch_gla(const GlaArgs& a, bool any_single, bool any_multi, cudaStream_t s) {
+  const int Dp = DPT * kGlaSlices;
+  const size_t smem = ((size_t)3 * kGlaBatch * Dp + kGlaBatch * kGlaCols + (size_t)kGlaSlices * kGlaBatch * kGlaCols) *
+                      sizeof(float);
+  dim3 grid(a.n_chunks, a.H, (a.Dv + kGlaCols - 1) / kGlaCols);
+  auto k0 = gla_chunk_kernel<T, DPT, 0>;
+  auto k1 = gla_chunk_kernel<T, DPT, 1>;
+  auto k3 = gla_chunk_kernel<T, DPT, 3>;
+  if (smem > 48 * 1024) {
+    cudaFuncSetAttribute(k0, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaFuncSetAttribute(k3, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  }
+  if (any_single) {
+    FTK_LAUNCH(k0, grid, kGlaSlices * 32, smem, s, a);
+    FTK_LAUNCH_CHECK("gla_scan (one chunk per request)");
+  }
+  if (any_multi) {
+    FTK_LAUNCH(k1, grid, kGlaSlices * 32, smem, s, a);
+    FTK_LAUNCH_CHECK("gla_scan (chunk contributions)");
+    const size_t DV = (size_t)a.D * a.Dv;
+    dim3 cgrid((unsigned)((DV + 255) / 256), a.n_segs, a.H);
+    FTK_LAUNCH(gla_carry_kernel, cgrid, 256, 0, s, a);
+    FTK_LAUNCH_CHECK("gla_scan (carry)");
+    FTK_LAUNCH(k3, grid, kGlaSlices * 32, smem, s, a);
+    FTK_LAUNCH_CHECK("gla_scan (chunk outputs)");
+  }
+  return 0;
+}
+
+}  // namespace ftk
+
+using namespace ftk;
+
+extern "C" int ftk_gla_scan(const void* q, long long q_stride, const void* k, long long k_stride, const void* v,
+                            long long v_stride, int dtype, const float* z, const float* z_bias, float tau,
+                            float q_scale, float* state, int n_slots, const int32_t* state_slots,
+                            const int32_t* seg_info, int n_segs, const int32_t* chunks, int n_chunks,
+                            const int32_t* seg_chunks, int any_single, int any_multi, float* carry,
+                            float* decay_prod, float* out, int n_tokens, int n_heads, int dim, int vdim,
+                            void* stream) {
+  FTK_REQUIRE(dtype_ok(dtype), "gla_scan: bad dtype %d", dtype);
+  FTK_REQUIRE(n_tokens >= 0 && n_segs >= 0 && n_chunks >= 0, "gla_scan: bad counts");
+  if (n_tokens == 0 || n_chunks == 0) return 0;
+  FTK_REQUIRE(n_heads >= 1 && n_heads <= 65535 && dim >= 1 && dim <= 256 && vdim >= 1 && vdim <= 65535 * kGlaCols,
+              "gla_scan: %d heads of %d key and %d value channels are not taken (at most 256 key channels)", n_heads,
+              dim, vdim);
+  FTK_REQUIRE(n_segs <= 65535, "gla_scan: too many segments");
+  FTK_REQUIRE(tau > 0.f, "gla_scan: tau must be positive");
+  FTK_REQUIRE(q && k && v && z && state && state_slots && seg_info && chunks && seg_chunks && out,
+              "gla_scan: null pointer");
+  FTK_REQUIRE(!any_multi || (carry && decay_prod), "gla_scan: portions of several chunks need scratch");
+  GlaArgs a;
+  a.q = q; a.k = k; a.v = v; a.q_stride = q_stride; a.k_stride = k_stride; a.v_stride = v_stride;
+  a.z = z; a.z_bias = z_bias; a.inv_tau = 1.f / tau; a.q_scale = q_scale;
+  a.state = state; a.state_slots = state_slots; a.seg_info = seg_info; a.chunks = chunks; a.seg_chunks = seg_chunks;
+  a.n_chunks = n_chunks; a.n_segs = n_segs; a.n_slots = n_slots; a.carry = carry; a.decay_prod = decay_prod;
+  a.out = out; a.H = n_heads; a.D = dim; a.Dv = vdim; a.n_tokens = n_tokens;
+  cudaStream_t s = (cudaStream_t)stream;
+  note_variant(any_multi ? "gla_scan: chunks side by side" : "gla_scan: one chunk per request");
+  const bool f32 = dtype == FTK_F32;
+  if (dim <= 32) return f32 ? launch_gla<float, 8>(a, any_single, any_multi, s) : launch_gla<__nv_bfloat16, 8>(a, any_single, any_multi, s);
+  if (dim <= 64) return f32 ? launch_gla<float, 16>(a, any_single, any_multi, s) : launch_gla<__nv_bfloat16, 16>(a, any_single, any_multi, s);
+  if (dim <= 128) return f32 ? launch_gla<float, 32>(a, any_single, any_multi, s) : launch_gla<__nv_bfloat16, 32>(a, any_single, any_multi, s);
+  return f32 ? launch_gla<float, 64>(a, any_single, any_multi, s) : launch_gla<__nv_bfloat16, 64>(a, any_single, any_multi, s);
+}

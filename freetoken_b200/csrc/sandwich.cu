@@ -1,0 +1,199 @@
+// Kernels of layers that norm a sub-layer on both sides, of gated head outputs and of capped logits.
+//
+//   * postnorm_add_norm: a sub-layer's output a is normed before it joins the 32-bit stream, and the
+//     stream is normed for the next sub-layer in the same pass:
+//         r <- r + a * rsqrt(mean(a^2) + eps_a) * w_a ;  out = r * rsqrt(mean(r^2) + eps_r) * w_r
+//     (w = 1 + weight in the Gemma form).  a is a dense row, or the sum over a token's expert routes
+//     (+ the shared expert's row), taken in 32 bits in route order.  Either half can be left out: without
+//     w_r only the stream is updated, with `rows` only those rows are normed and the stream stays.
+//   * gated_heads: per (token, head) row, an optional RMS norm over the head (plain weight) and a gate taken
+//     element by element from another projection of the same token: y = norm(x) * act(g), act = sigmoid or
+//     silu.  The input is 32-bit (a recurrent layer's output) or the engine's type (attention output, in place).
+//   * softcap: x <- cap * tanh(x / cap) on float32 logits.
+#include "common.cuh"
+
+namespace ftk {
+
+struct SandwichArgs {
+  const void* x;          // [*, hidden] dense rows of the sub-layer's output, or the experts' rows when route_pos is set
+  const int32_t* route_pos;
+  int top_k, n_routes;
+  const void* shared;     // [*, hidden] or null (with route_pos)
+  const float* post_w;    // [hidden]
+  float* residual;        // [*, hidden]
+  const float* pre_w;     // [hidden] or null: no norm of the stream, no out
+  void* out;              // [n_rows, hidden] of the engine's type, or null
+  float* out_f32;         // [n_rows, hidden] or null
+  const int32_t* rows;    // or null
+  int n_rows, hidden;
+  float post_eps, pre_eps;
+  int post_gemma, pre_gemma;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) postnorm_add_norm_kernel(SandwichArgs a) {
+  pdl_wait();
+  pdl_trigger();
+  extern __shared__ float zrow[];
+  __shared__ float red[33];
+  const int r = blockIdx.x;
+  const int src_row = a.rows ? a.rows[r] : r;
+  const size_t src = (size_t)src_row * a.hidden, dst = (size_t)r * a.hidden;
+  const T* x = (const T*)a.x;
+  const T* shared = (const T*)a.shared;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < a.hidden; i += blockDim.x) {
+    float v;
+    if (a.route_pos) {
+      v = 0.f;
+      for (int j = 0; j < a.top_k; ++j) {  // route order
+        const int p = a.route_pos[(size_t)src_row * a.top_k + j];
+        if (p >= 0 && p < a.n_routes) v += to_float(x[(size_t)p * a.hidden + i]);
+      }
+      if (shared) v += to_float(shared[src + i]);
+    } else {
+      v = to_float(x[src + i]);
+    }
+    zrow[i] = v;
+    ss += v * v;
+  }
+  ss = block_sum(ss, red);
+  const float inv_a = rsqrtf(ss / (float)a.hidden + a.post_eps);
+  float ss2 = 0.f;
+  for (int i = threadIdx.x; i < a.hidden; i += blockDim.x) {
+    const float w = a.post_gemma ? 1.f + a.post_w[i] : a.post_w[i];
+    const float z = a.residual[src + i] + zrow[i] * inv_a * w;
+    if (!a.rows) a.residual[src + i] = z;
+    zrow[i] = z;
+    ss2 += z * z;
+  }
+  if (!a.pre_w) return;
+  ss2 = block_sum(ss2, red);
+  const float inv_r = rsqrtf(ss2 / (float)a.hidden + a.pre_eps);
+  T* out = (T*)a.out;
+  for (int i = threadIdx.x; i < a.hidden; i += blockDim.x) {
+    const float w = a.pre_gemma ? 1.f + a.pre_w[i] : a.pre_w[i];
+    const T y = from_float<T>(zrow[i] * inv_r * w);
+    if (out) out[dst + i] = y;
+    if (a.out_f32) a.out_f32[dst + i] = to_float(y);
+  }
+}
+
+// One warp per (token, head).  x: [T, n_heads, x_stride] (XT), g: row t at g + t * g_stride, head h at + h * dim,
+// out: [T, n_heads, out_stride] (T).  Columns past `dim` of a padded destination are left as they are.
+template <typename XT, typename T>
+__global__ void gated_heads_kernel(const XT* __restrict__ x, int x_stride, const T* __restrict__ g, long long g_stride,
+                                   const float* __restrict__ norm_w, float eps, int act, T* __restrict__ out,
+                                   int out_stride, int n_tokens, int n_heads, int dim) {
+  pdl_wait();
+  pdl_trigger();
+  const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (w >= (long long)n_tokens * n_heads) return;
+  const int lane = threadIdx.x & 31;
+  const long long t = w / n_heads;
+  const int h = (int)(w % n_heads);
+  const XT* xr = x + (size_t)w * x_stride;
+  const T* gr = g + t * g_stride + (size_t)h * dim;
+  T* o = out + (size_t)w * out_stride;
+  float inv = 1.f;
+  if (norm_w) {
+    float ss = 0.f;
+    for (int d = lane; d < dim; d += 32) {
+      const float v = to_float(xr[d]);
+      ss += v * v;
+    }
+    ss = warp_sum(ss);
+    inv = rsqrtf(ss / (float)dim + eps);
+  }
+  for (int d = lane; d < dim; d += 32) {
+    float v = to_float(xr[d]) * inv;
+    if (norm_w) v *= norm_w[d];
+    const float gv = to_float(gr[d]);
+    const float s = 1.f / (1.f + expf(-gv));
+    o[d] = from_float<T>(v * (act == FTK_GATE_SILU ? gv * s : s));
+  }
+}
+
+__global__ void softcap_kernel(float* x, long long n, float cap) {
+  pdl_wait();
+  pdl_trigger();
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  const float inv = 1.f / cap;
+  for (; i < n; i += stride) x[i] = cap * tanhf(x[i] * inv);
+}
+
+}  // namespace ftk
+
+using namespace ftk;
+
+extern "C" int ftk_postnorm_add_norm(const void* x, int dtype, const int32_t* route_pos, int top_k, int n_routes,
+                                     const void* shared, const float* post_w, float post_eps, int post_gemma,
+                                     float* residual, const float* pre_w, float pre_eps, int pre_gemma, void* out,
+                                     float* out_f32, const int32_t* rows, int n_rows, int hidden, void* stream) {
+  FTK_REQUIRE(dtype_ok(dtype), "postnorm_add_norm: bad dtype %d", dtype);
+  FTK_REQUIRE(n_rows >= 0 && hidden >= 1, "postnorm_add_norm: bad sizes");
+  if (n_rows == 0) return 0;
+  FTK_REQUIRE(x && post_w && residual, "postnorm_add_norm: null pointer");
+  FTK_REQUIRE(!route_pos || (top_k >= 1 && n_routes >= 0), "postnorm_add_norm: bad route counts");
+  FTK_REQUIRE(pre_w || (!out && !out_f32), "postnorm_add_norm: an output needs the weight of the stream's norm");
+  FTK_REQUIRE(!pre_w || out || out_f32, "postnorm_add_norm: the stream's norm needs an output");
+  FTK_REQUIRE(!rows || pre_w, "postnorm_add_norm: rows are picked for an output only");
+  SandwichArgs a;
+  a.x = x; a.route_pos = route_pos; a.top_k = top_k; a.n_routes = n_routes; a.shared = route_pos ? shared : nullptr;
+  a.post_w = post_w; a.residual = residual; a.pre_w = pre_w; a.out = out; a.out_f32 = out_f32; a.rows = rows;
+  a.n_rows = n_rows; a.hidden = hidden; a.post_eps = post_eps; a.pre_eps = pre_eps;
+  a.post_gemma = post_gemma; a.pre_gemma = pre_gemma;
+  const size_t smem = (size_t)hidden * sizeof(float);
+  FTK_REQUIRE(smem <= 200 * 1024, "postnorm_add_norm: rows of %d elements do not fit shared memory", hidden);
+  if (dtype == FTK_F32) {
+    auto kern = postnorm_add_norm_kernel<float>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    FTK_LAUNCH(kern, n_rows, 256, smem, stream, a);
+  } else {
+    auto kern = postnorm_add_norm_kernel<__nv_bfloat16>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    FTK_LAUNCH(kern, n_rows, 256, smem, stream, a);
+  }
+  FTK_LAUNCH_CHECK("postnorm_add_norm");
+  return 0;
+}
+
+extern "C" int ftk_gated_heads(const void* x, int x_f32, int x_stride, const void* gates, long long gate_stride,
+                               const float* norm_w, float eps, int act, void* out, int out_stride, int dtype,
+                               int n_tokens, int n_heads, int dim, void* stream) {
+  FTK_REQUIRE(dtype_ok(dtype), "gated_heads: bad dtype %d", dtype);
+  FTK_REQUIRE(act == FTK_GATE_SIGMOID || act == FTK_GATE_SILU, "gated_heads: unknown gate %d", act);
+  FTK_REQUIRE(n_tokens >= 0 && n_heads >= 1 && dim >= 1 && x_stride >= dim && out_stride >= dim &&
+                  gate_stride >= (long long)n_heads * dim,
+              "gated_heads: bad sizes");
+  if (n_tokens == 0) return 0;
+  FTK_REQUIRE(x && gates && out, "gated_heads: null pointer");
+  const long long rows = (long long)n_tokens * n_heads;
+  const int warps = 8;
+  const unsigned blocks = (unsigned)((rows + warps - 1) / warps);
+  if (dtype == FTK_F32) {
+    FTK_LAUNCH((gated_heads_kernel<float, float>), blocks, warps * 32, 0, stream, (const float*)x, x_stride,
+               (const float*)gates, gate_stride, norm_w, eps, act, (float*)out, out_stride, n_tokens, n_heads, dim);
+  } else if (x_f32) {
+    FTK_LAUNCH((gated_heads_kernel<float, __nv_bfloat16>), blocks, warps * 32, 0, stream, (const float*)x, x_stride,
+               (const __nv_bfloat16*)gates, gate_stride, norm_w, eps, act, (__nv_bfloat16*)out, out_stride, n_tokens,
+               n_heads, dim);
+  } else {
+    FTK_LAUNCH((gated_heads_kernel<__nv_bfloat16, __nv_bfloat16>), blocks, warps * 32, 0, stream,
+               (const __nv_bfloat16*)x, x_stride, (const __nv_bfloat16*)gates, gate_stride, norm_w, eps, act,
+               (__nv_bfloat16*)out, out_stride, n_tokens, n_heads, dim);
+  }
+  FTK_LAUNCH_CHECK("gated_heads");
+  return 0;
+}
+
+extern "C" int ftk_softcap_f32(float* x, long long n, float cap, void* stream) {
+  FTK_REQUIRE(n >= 0 && cap > 0.f, "softcap: bad arguments");
+  if (n == 0) return 0;
+  FTK_REQUIRE(x, "softcap: null pointer");
+  const unsigned blocks = (unsigned)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
+  FTK_LAUNCH(softcap_kernel, blocks, 256, 0, stream, x, n, cap);
+  FTK_LAUNCH_CHECK("softcap");
+  return 0;
+}

@@ -48,9 +48,9 @@ from . import library
 
 F32, BF16 = 0, 1
 ACT_SILU, ACT_SWIGLUOAI = 0, 1
-SCORE_SIGMOID, SCORE_SOFTMAX = 0, 1
+SCORE_SIGMOID, SCORE_SOFTMAX, SCORE_SOFTMAX_OF_CHOSEN = 0, 1, 2
 ACT_CODES = {"silu": ACT_SILU, "swigluoai": ACT_SWIGLUOAI}
-SCORE_CODES = {"sigmoid": SCORE_SIGMOID, "softmax": SCORE_SOFTMAX}
+SCORE_CODES = {"sigmoid": SCORE_SIGMOID, "softmax": SCORE_SOFTMAX, "softmax_of_chosen": SCORE_SOFTMAX_OF_CHOSEN}
 
 _vp = ctypes.c_void_p
 _i = ctypes.c_int
@@ -74,7 +74,7 @@ class _StreamNorm(ctypes.Structure):
 
 
 class _AttnExtras(ctypes.Structure):
-    _fields_ = [("dist_bias", _vp), ("dist_len", _i), ("kv_split", _i)]
+    _fields_ = [("dist_bias", _vp), ("dist_len", _i), ("kv_split", _i), ("has_sink", _i), ("sink_logit", _f)]
 
 
 _SIGNATURES = {
@@ -130,6 +130,11 @@ _SIGNATURES = {
     "ftk_set_moe_pairs": [_i],
     "ftk_debug_set_status": [_i, _i],
     "ftk_variant_counts": [ctypes.c_char_p, _i, _i],
+    "ftk_softcap_f32": [_vp, ctypes.c_longlong, _f, _vp],
+    "ftk_postnorm_add_norm": [_vp, _i, _vp, _i, _i, _vp, _vp, _f, _i, _vp, _vp, _f, _i, _vp, _vp, _vp, _i, _i, _vp],
+    "ftk_gated_heads": [_vp, _i, _i, _vp, ctypes.c_longlong, _vp, _f, _i, _vp, _i, _i, _i, _i, _i, _vp],
+    "ftk_gla_scan": [_vp, ctypes.c_longlong, _vp, ctypes.c_longlong, _vp, ctypes.c_longlong, _i, _vp, _vp, _f, _f,
+                     _vp, _i, _vp, _vp, _i, _vp, _i, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
 }
 _bound = False
 _launches = 0
@@ -410,7 +415,8 @@ def paged_attention(q: torch.Tensor, k_slab: torch.Tensor, v_slab: torch.Tensor,
                     items: torch.Tensor, n_items: int, part_o: Optional[torch.Tensor],
                     part_ml: Optional[torch.Tensor], out: torch.Tensor, tile_rows: int, scale: float,
                     window: Optional[int], sel: Optional[torch.Tensor] = None, block_size: int = 0,
-                    few_rows: bool = False, dist_bias: Optional[torch.Tensor] = None, kv_split: int = 1) -> None:
+                    few_rows: bool = False, dist_bias: Optional[torch.Tensor] = None, kv_split: int = 1,
+                    sink: Optional[float] = None) -> None:
     """Causal softmax attention of the step's queries over the paged keys and values.
 
     ``q, out [T, Hq, D]``; slabs ``[pages, Hkv, page_size, D]``; ``block_table [rows, width]``
@@ -437,6 +443,10 @@ def paged_attention(q: torch.Tensor, k_slab: torch.Tensor, v_slab: torch.Tensor,
     ``Hkv * kv_split`` heads.  Not with the tcgen05 kernels.
     Of the tcgen05 kernels the ones with one query tile a piece (128 rows, or at most 16) take the bias; with
     one slab for keys and values their key tile in shared memory serves both products.
+
+    ``sink`` (a logit, or None): the softmax's denominator also holds ``e^sink``, a key without a value, so a
+    row's weights are ``e^(s_j) / (e^sink + sum_i e^(s_i))``.  A tile that is split along the keys gets it once,
+    in the merge.  Not with the tcgen05 kernels, nor with block selection.
     """
     T, Hq, D = q.shape
     pages, Hkv, P, D2 = k_slab.shape
@@ -456,13 +466,13 @@ def paged_attention(q: torch.Tensor, k_slab: torch.Tensor, v_slab: torch.Tensor,
         raise KernelError(f"paged_attention: few_rows goes with tiles of 16 rows, got {tile_rows}")
     if tile_rows in (128, 256) or few_rows:
         # bfloat16 steps on the tcgen05 kernels: one query tile per CTA, a pair of them, or tiles of a few rows
-        if sel is not None or window or q.dtype != torch.bfloat16:
-            raise KernelError("paged_attention: the tcgen05 kernels take bfloat16 without window or block selection")
+        if sel is not None or window or q.dtype != torch.bfloat16 or sink is not None:
+            raise KernelError("paged_attention: the tcgen05 kernels take bfloat16 without window, sink or block selection")
         if dist_bias is not None:  # the forms with one query tile a piece (128 rows, or at most 16) take it
             if tile_rows == 256 or dist_bias.dim() != 2 or dist_bias.shape[0] != Hq:
                 raise KernelError("paged_attention: of the tcgen05 kernels the ones with one query tile a piece take a "
                                   "distance bias [Hq, L]")
-            ex = _AttnExtras(_dev(dist_bias, "dist_bias", torch.float32), dist_bias.shape[1], 1)
+            ex = _AttnExtras(_dev(dist_bias, "dist_bias", torch.float32), dist_bias.shape[1], 1, 0, 0.0)
             _check(_lib().ftk_paged_attention_tc_ex(
                 _dev(q, "q"), _dev(k_slab, "k_slab"), _dev(v_slab, "v_slab"),
                 _dev(block_table, "block_table", torch.int32), block_table.shape[1],
@@ -485,6 +495,8 @@ def paged_attention(q: torch.Tensor, k_slab: torch.Tensor, v_slab: torch.Tensor,
             "paged_attention (tcgen05)", 2 if n_slots else 1)
         return
     if sel is not None:
+        if sink is not None:
+            raise KernelError("paged_attention: a sink cannot be combined with block selection")
         if sel.dim() != 3 or sel.shape[0] < T or sel.shape[1] != Hkv or block_size < 1:
             raise KernelError("paged_attention: sel must be [T, Hkv, topk] with a positive block_size")
         _check(_lib().ftk_paged_attention_sparse(
@@ -497,11 +509,11 @@ def paged_attention(q: torch.Tensor, k_slab: torch.Tensor, v_slab: torch.Tensor,
             _dev(sel, "sel", torch.int32), sel.shape[2], int(block_size), _stream()),
             "paged_attention (block-sparse)", 2 if n_slots else 1)
         return
-    if dist_bias is not None or kv_split > 1:
+    if dist_bias is not None or kv_split > 1 or sink is not None:
         if dist_bias is not None and (dist_bias.dim() != 2 or dist_bias.shape[0] != Hq or dist_bias.shape[1] < 1):
             raise KernelError("paged_attention: dist_bias must be [Hq, L]")
         ex = _AttnExtras(_dev(dist_bias, "dist_bias", torch.float32), dist_bias.shape[1] if dist_bias is not None else 0,
-                         kv_split)
+                         kv_split, 0 if sink is None else 1, 0.0 if sink is None else float(sink))
         _check(_lib().ftk_paged_attention_ex(
             _dev(q, "q"), _dev(k_slab, "k_slab"), _dev(v_slab, "v_slab"), _code(q, "q"),
             _dev(block_table, "block_table", torch.int32), block_table.shape[1],
@@ -509,7 +521,7 @@ def paged_attention(q: torch.Tensor, k_slab: torch.Tensor, v_slab: torch.Tensor,
             _dev(items, "items", torch.int32), n_items,
             _dev(part_o, "part_o", torch.float32), _dev(part_ml, "part_ml", torch.float32), n_slots,
             _dev(out, "out"), Hq, Hkv, D, P, pages, tile_rows, float(scale),
-            int(window) if window else 0, ctypes.byref(ex), _stream()), "paged_attention (distance bias)",
+            int(window) if window else 0, ctypes.byref(ex), _stream()), "paged_attention (with options)",
             2 if n_slots else 1)
         return
     _check(_lib().ftk_paged_attention(
@@ -575,6 +587,7 @@ def router_topk(logits: torch.Tensor, bias: Optional[torch.Tensor], top_k: int, 
 
     sigmoid: ``s = sigmoid(l)``; choice by ``s + bias``; ``w = s[ids] / (sum + 1e-20) * scale``.
     softmax: ``s = softmax(l)``; choice by ``s (+ bias)``; ``w = s[ids] / sum * scale``.
+    softmax_of_chosen: the bias belongs to the logit: choice by ``l + bias``; ``w = softmax((l + bias)[ids]) * scale``.
     The largest goes first; the lower expert index wins a tie.
 
     With ``n_parts > 1`` the logits come as ``[T, n_parts * E]``: a token's logit of expert ``e`` is the
@@ -668,6 +681,19 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[t
         torch.matmul(x.as_strided((P, K), (K, 1)), w.t(), out=out.as_strided((P, N), (N, 1)))
     else:
         torch.matmul(x, w.t(), out=out)
+
+
+def linear_f32(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """``out = x @ w^T`` kept as the 32-bit sums of the library's product (``out`` float32), for a result
+    that enters 32-bit arithmetic (a recurrence's decay logits).  ``x`` may be a view of adjacent columns."""
+    T, K = x.shape
+    N = w.shape[0]
+    if w.shape != (N, K) or out.shape != (T, N) or out.dtype != torch.float32 or x.dtype != w.dtype:
+        raise KernelError("linear_f32: shapes or dtypes do not agree")
+    if x.dtype == torch.float32:
+        torch.matmul(x, w.t(), out=out)
+    else:
+        torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
 
 
 def _room(t: torch.Tensor) -> int:
@@ -929,3 +955,119 @@ def table_route(token_ids: torch.Tensor, table: torch.Tensor, n_experts: int, id
 def scale_(x: torch.Tensor, s: float) -> None:
     """``x *= s`` for a float32 tensor."""
     _check(_lib().ftk_scale_f32(_dev(x, "x", torch.float32), x.numel(), float(s), _stream()), "scale")
+
+
+def softcap_(x: torch.Tensor, cap: float) -> None:
+    """``x <- cap * tanh(x / cap)`` for a float32 tensor."""
+    if not cap > 0:
+        raise KernelError("softcap: the cap must be positive")
+    _check(_lib().ftk_softcap_f32(_dev(x, "x", torch.float32), x.numel(), float(cap), _stream()), "softcap")
+
+
+GATE_CODES = {"sigmoid": 0, "silu": 1}
+
+
+def postnorm_add_norm(x: torch.Tensor, routed, post_weight: torch.Tensor, post_eps: float, post_gemma: bool,
+                      residual: torch.Tensor, pre_weight: Optional[torch.Tensor] = None, pre_eps: float = 0.0,
+                      pre_gemma: bool = True, out: Optional[torch.Tensor] = None,
+                      out_f32: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None) -> None:
+    """A sub-layer's output joins the 32-bit stream through an RMS norm of its own, and the stream is normed
+    for the next sub-layer in the same pass:
+
+    ``residual += a * rsqrt(mean(a^2) + post_eps) * w_post``, then (with ``pre_weight``)
+    ``out = residual * rsqrt(mean(residual^2) + pre_eps) * w_pre`` (``w = 1 + weight`` in the Gemma form).
+
+    ``a`` is row ``t`` of ``x``, or, with ``routed = (route_pos, top_k, shared or None)``, the 32-bit sum
+    ``sum_j x[route_pos[t * top_k + j]] (+ shared[t])`` over a token's expert routes in route order.  With
+    ``rows`` only those rows are normed into ``out`` and the stream stays as it is (``out[i]`` belongs to
+    ``rows[i]``).  ``out_f32`` receives ``float32(out)``."""
+    H = residual.shape[-1]
+    n_rows = rows.shape[0] if rows is not None else residual.numel() // H
+    if post_weight.shape != (H,) or x.shape[-1] != H or (pre_weight is not None and pre_weight.shape != (H,)):
+        raise KernelError("postnorm_add_norm: widths do not agree")
+    if pre_weight is None and (out is not None or out_f32 is not None or rows is not None):
+        raise KernelError("postnorm_add_norm: an output needs the weight of the stream's norm")
+    if pre_weight is not None and out is None:
+        raise KernelError("postnorm_add_norm: the stream's norm needs an output")
+    if out is not None and (out.numel() != n_rows * H or out.dtype != x.dtype):
+        raise KernelError("postnorm_add_norm: out has the wrong size or dtype")
+    if out_f32 is not None and out_f32.numel() != n_rows * H:
+        raise KernelError("postnorm_add_norm: out_f32 has the wrong size")
+    pos, top_k, shared, n_routes = None, 0, None, 0
+    if routed is not None:
+        pos, top_k, shared = routed
+        n_routes = x.shape[0]
+        if pos.numel() < residual.numel() // H * top_k or (shared is not None and shared.dtype != x.dtype):
+            raise KernelError("postnorm_add_norm: routes do not match the rows")
+    elif x.numel() < residual.numel():
+        raise KernelError("postnorm_add_norm: x has fewer rows than the stream")
+    _check(_lib().ftk_postnorm_add_norm(
+        _dev(x, "x"), _code(x, "x"), _dev(pos, "route_pos", torch.int32), int(top_k), int(n_routes),
+        _dev(shared, "shared"), _dev(post_weight, "post_weight", torch.float32), float(post_eps),
+        1 if post_gemma else 0, _dev(residual, "residual", torch.float32),
+        _dev(pre_weight, "pre_weight", torch.float32), float(pre_eps), 1 if pre_gemma else 0, _dev(out, "out"),
+        _dev(out_f32, "out_f32", torch.float32), _dev(rows, "rows", torch.int32), n_rows, H, _stream()),
+        "postnorm_add_norm")
+
+
+def gated_heads(x: torch.Tensor, gates: torch.Tensor, out: torch.Tensor, dim: int, act: str = "sigmoid",
+                norm_weight: Optional[torch.Tensor] = None, eps: float = 0.0) -> None:
+    """``out[t, h, :dim] = norm(x[t, h, :dim]) * act(gates[t, h * dim + :dim])``: a gate taken element by
+    element from another projection of the same token, after an optional RMS norm over each head
+    (``norm_weight [dim]``, plain weight).  ``x [T, heads, >= dim]`` is float32 or of ``out``'s dtype;
+    ``out [T, heads, >= dim]`` may be ``x`` itself; columns past ``dim`` are left alone.  ``gates
+    [T, heads * dim]`` may be a view of adjacent columns of a wider row-major tensor."""
+    T, H, xs = x.shape
+    if out.shape[:2] != (T, H) or out.shape[2] < dim or xs < dim or gates.shape != (T, H * dim):
+        raise KernelError("gated_heads: shapes do not agree")
+    if gates.dtype != out.dtype or gates.stride(1) != 1 or x.dtype not in (torch.float32, out.dtype):
+        raise KernelError("gated_heads: gates must be of out's dtype with adjacent columns, x float32 or out's dtype")
+    if norm_weight is not None and norm_weight.shape != (dim,):
+        raise KernelError("gated_heads: norm_weight must be [dim]")
+    if act not in GATE_CODES:
+        raise KernelError(f"gated_heads: unknown gate '{act}'")
+    if not x.is_contiguous() or not out.is_contiguous():
+        raise KernelError("gated_heads: x and out must be contiguous")
+    _check(_lib().ftk_gated_heads(
+        _dev(x, "x"), 1 if x.dtype == torch.float32 else 0, xs, gates.data_ptr(),
+        gates.stride(0) if T > 1 else H * dim, _dev(norm_weight, "norm_weight", torch.float32), float(eps),
+        GATE_CODES[act], _dev(out, "out"), out.shape[2], _code(out, "out"), T, H, dim, _stream()), "gated_heads")
+
+
+def gla_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor, z_bias: Optional[torch.Tensor],
+             tau: float, q_scale: float, state: torch.Tensor, state_slots: torch.Tensor, seg_info: torch.Tensor,
+             n_segs: int, chunks: torch.Tensor, n_chunks: int, seg_chunks: torch.Tensor, any_single: bool,
+             any_multi: bool, carry: Optional[torch.Tensor], decay_prod: Optional[torch.Tensor],
+             out: torch.Tensor) -> None:
+    """Gated linear attention of the step's tokens, per (request, head):
+    ``S <- diag(a_t) S + k_t v_t^T``, ``o_t = S^T (q_t q_scale)``, ``a_t = sigmoid(z_t + z_bias)^(1 / tau)``.
+
+    ``q, k [T, H * D]`` and ``v [T, H * Dv]`` of the engine's dtype (views of adjacent columns of a wider
+    tensor are fine); ``z [T, H * D]`` float32; ``state [slots, H, D, Dv]`` float32, read from and left in
+    the slot ``state_slots[segment]`` (a segment with ``kv_len == q_len`` starts from zero);
+    ``chunks [n, 4]`` / ``seg_chunks [S, 2]`` from :func:`freetoken_b200.parts.gla.chunk_list`; ``carry
+    [n, H, D, Dv]`` and ``decay_prod [n, H, D]`` float32 scratch for segments of several chunks;
+    ``out [T, H, Dv]`` float32."""
+    T = out.shape[0]
+    H, D, Dv = state.shape[1], state.shape[2], state.shape[3]
+    if q.shape != (T, H * D) or k.shape != (T, H * D) or v.shape != (T, H * Dv) or out.shape != (T, H, Dv) \
+            or z.shape != (T, H * D):
+        raise KernelError("gla_scan: shapes do not agree")
+    if q.dtype != k.dtype or q.dtype != v.dtype or q.stride(1) != 1 or k.stride(1) != 1 or v.stride(1) != 1:
+        raise KernelError("gla_scan: q, k, v must share a dtype and have adjacent columns")
+    if z_bias is not None and z_bias.numel() != H * D:
+        raise KernelError("gla_scan: z_bias must hold H * D entries")
+    if any_multi and (carry is None or decay_prod is None or carry.numel() < n_chunks * H * D * Dv
+                      or decay_prod.numel() < n_chunks * H * D):
+        raise KernelError("gla_scan: scratch for segments of several chunks is missing or too small")
+    if chunks.numel() < 4 * n_chunks or seg_chunks.numel() < 2 * n_segs:
+        raise KernelError("gla_scan: chunk lists too short")
+    launches = (1 if any_single else 0) + (3 if any_multi else 0)
+    _check(_lib().ftk_gla_scan(
+        q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), _code(q, "q"),
+        _dev(z, "z", torch.float32), _dev(z_bias, "z_bias", torch.float32), float(tau), float(q_scale),
+        _dev(state, "state", torch.float32), state.shape[0], _dev(state_slots, "state_slots", torch.int32),
+        _dev(seg_info, "seg_info", torch.int32), n_segs, _dev(chunks, "chunks", torch.int32), n_chunks,
+        _dev(seg_chunks, "seg_chunks", torch.int32), 1 if any_single else 0, 1 if any_multi else 0,
+        _dev(carry, "carry", torch.float32), _dev(decay_prod, "decay_prod", torch.float32),
+        _dev(out, "out", torch.float32), T, H, D, Dv, _stream()), "gla_scan", max(1, launches))

@@ -23,7 +23,7 @@ import torch
 from ..config.spec import ModelSpec, ParamSpec, PartSpec
 from ..errors import ConfigError
 from ..parts import BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, BuildEnv, Part, StepState
-from ..parts.base import StreamSum, as_rows, nvtx_range
+from ..parts.base import NormedSum, StreamSum, as_rows, nvtx_range
 
 
 def _walk(prefix: str, part: Part, out: Dict[str, Tuple[Part, str, ParamSpec]]) -> None:
@@ -148,6 +148,9 @@ class Model:
             if e.add_embedding or e.add_pass_vector is not None:
                 # fed into the stream with whatever the layer before left to be added: the entry's first norm
                 # (or, for a norm that cannot, one launch of its own) takes all of it in one 32-bit sum
+                if isinstance(x, NormedSum):  # it joins the stream through a norm of its own: add it now
+                    x.fold(residual)
+                    x = None
                 x = StreamSum.of(x) if x is not None else StreamSum()
                 if e.add_embedding:
                     x.add_rows_of(self.embedding.table(), step.token_ids)

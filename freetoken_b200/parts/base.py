@@ -270,10 +270,37 @@ class StreamSum:
         ops.stream_add_norm(residual, None, **self.kernel_args(residual))
 
 
+class NormedSum:
+    """A sub-layer output that joins the stream through a norm of its own: ``norm(x)`` is still to be added.
+    ``x`` is a tensor or a :class:`RouteSum`, ``norm`` an RMS norm part (``params["weight"]``, ``eps``,
+    ``gemma``).  A norm with ``takes_normed_sum`` adds it in the pass that norms the stream; for any other
+    consumer :meth:`fold` adds it first."""
+
+    def __init__(self, x: Any, norm: Any):
+        self.x, self.norm = x, norm
+
+    def kernel_args(self):
+        """``(rows, routed)`` as ``ops.postnorm_add_norm`` takes them."""
+        if isinstance(self.x, RouteSum):
+            return self.x.y, (self.x.pos, self.x.top_k, self.x.shared)
+        return self.x, None
+
+    def fold(self, residual: torch.Tensor) -> None:
+        from ..kernels import ops
+
+        rows, routed = self.kernel_args()
+        ops.postnorm_add_norm(rows, routed, self.norm.params["weight"], self.norm.eps, self.norm.gemma, residual)
+
+
 def as_rows(x: Any, consumer: Any = None, residual: Optional[torch.Tensor] = None) -> Any:
     """``x`` as the consumer can take it: a :class:`RouteSum` stays one only for a norm that says it
     takes one; a :class:`StreamSum` stays one only for a norm with ``takes_stream_sum`` and is otherwise
     added to ``residual`` at once (nothing is then left to hand on)."""
+    if isinstance(x, NormedSum) and not getattr(consumer, "takes_normed_sum", False):
+        if residual is None:
+            raise ConfigError("a NormedSum needs the stream to be added to")
+        x.fold(residual)
+        return None
     if isinstance(x, StreamSum) and not getattr(consumer, "takes_stream_sum", False):
         if residual is None:
             raise ConfigError("a StreamSum needs the stream to be added to")
@@ -287,6 +314,7 @@ def as_rows(x: Any, consumer: Any = None, residual: Optional[torch.Tensor] = Non
 class Norm(Part):
     takes_route_sum: bool = False  # add_forward accepts a RouteSum as x
     takes_stream_sum: bool = False  # add_forward accepts a StreamSum as x
+    takes_normed_sum: bool = False  # add_forward accepts a NormedSum as x
 
     def forward(self, x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         """``out = norm(x)`` row by row."""

@@ -9,6 +9,10 @@ the next layer's first norm.  The residual stream is 32-bit.
 and ``a + f`` travels to the next layer's norm as a :class:`StreamSum`, so that both are added to
 the 32-bit stream in 32 bits, by the kernel that norms.  A layer without feed-forward names the
 feed-forward kind ``none``.
+
+``sandwich_residual``: every sub-layer is normed on both sides, ``r += N_1b(mixer(N_1(r)))``, then
+``r += N_2b(ffn(N_2(r)))``.  The norm behind a sub-layer, the sum into the 32-bit stream and the norm in
+front of the next sub-layer are one kernel: a sub-layer's output travels on as a :class:`NormedSum`.
 """
 
 from __future__ import annotations
@@ -18,8 +22,9 @@ from typing import Any, Dict, Optional
 import torch
 
 from ..config.spec import PartSpec
-from .base import (BLOCKS, FEED_FORWARDS, NORMS, Block, BuildEnv, FeedForward, Mixer, Part, StepState, StreamSum, as_rows,
-                   nvtx_range)
+from ..errors import ConfigError
+from .base import (BLOCKS, FEED_FORWARDS, NORMS, Block, BuildEnv, FeedForward, Mixer, NormedSum, Part, StepState, StreamSum,
+                   as_rows, nvtx_range)
 
 
 @BLOCKS.register("prenorm_residual")
@@ -104,3 +109,52 @@ class ParallelResidualBlock(Block):
             with nvtx_range(f"feed-forward {self.ffn.kind}"):
                 out.add(lazy(h, step, h_f32=None) if lazy is not None else self.ffn.forward(h, step))
         return out
+
+
+@BLOCKS.register("sandwich_residual")
+class SandwichResidualBlock(Block):
+    """params: ``hidden``, ``norm`` (PartSpec used for all four norms; an RMS norm), ``norm_names`` (weight-name
+    parts of the norms in front of and behind the mixer, in front of and behind the feed-forward)."""
+
+    def __init__(self, spec: PartSpec, env: BuildEnv, mixer: Mixer, ffn: FeedForward,
+                 mixer_name: str, ffn_name: str):
+        super().__init__(spec, env, mixer, ffn, mixer_name, ffn_name)
+        self.hidden = int(spec["hidden"])
+        self.has_ffn = not isinstance(ffn, NoFeedForward)
+        self.names = tuple(spec.get("norm_names", ("norm1", "norm1b", "norm2", "norm2b")))
+        self.mixer_in = NORMS.build(spec["norm"], env)
+        self.mixer_out = NORMS.build(spec["norm"], env)
+        self.ffn_in = NORMS.build(spec["norm"], env) if self.has_ffn else None
+        self.ffn_out = NORMS.build(spec["norm"], env) if self.has_ffn else None
+        for n in (self.mixer_in, self.mixer_out):
+            if not getattr(n, "takes_normed_sum", False):
+                raise ConfigError("sandwich_residual: its norms are RMS norms (they take a NormedSum)")
+
+    def children(self) -> Dict[str, Part]:
+        out = {self.names[0]: self.mixer_in, self.mixer_name: self.mixer, self.names[1]: self.mixer_out}
+        if self.has_ffn:
+            out.update({self.names[2]: self.ffn_in, self.ffn_name: self.ffn, self.names[3]: self.ffn_out})
+        return out
+
+    def workspace_bytes(self, n_tokens: int) -> int:
+        item = 4 if self.env.dtype == torch.float32 else 2
+        return n_tokens * self.hidden * (2 * item + 4)
+
+    def forward(self, x, residual: torch.Tensor, step: StepState, cache: Any, writes_cache: bool):
+        T = residual.shape[0]
+        ws, dt, cap = self.env.workspace, self.env.dtype, self.env.max_step_tokens
+        h = ws.get("block.h", (T, self.hidden), dt, (cap, self.hidden))
+        self.mixer_in.add_forward(as_rows(x, self.mixer_in, residual), residual, h)
+        with nvtx_range(f"mixer {self.mixer.kind}"):
+            a = NormedSum(self.mixer.forward(h, step, cache, writes_cache), self.mixer_out)
+        if not self.has_ffn:
+            return a
+        h2 = ws.get("block.h2", (T, self.hidden), dt, (cap, self.hidden))
+        h32 = None
+        if self.ffn.f32_input_needed(T) and dt != torch.float32:
+            h32 = ws.get("block.h2_f32", (T, self.hidden), torch.float32, (cap, self.hidden))
+        self.ffn_in.add_forward(a, residual, h2, out_f32=h32)
+        lazy = getattr(self.ffn, "forward_lazy", None)
+        with nvtx_range(f"feed-forward {self.ffn.kind}"):
+            f = lazy(h2, step, h_f32=h32) if lazy is not None else self.ffn.forward(h2, step, h_f32=h32)
+        return NormedSum(f, self.ffn_out)

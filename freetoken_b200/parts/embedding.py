@@ -29,19 +29,23 @@ from .base import EMBEDDINGS, HEADS, BuildEnv, Embedding, Head
 
 @EMBEDDINGS.register("token_embedding")
 class TokenEmbedding(Embedding):
-    """params: ``vocab``, ``hidden``, ``init_std`` (spread of random weights, 0.02)."""
+    """params: ``vocab``, ``hidden``, ``init_std`` (spread of random weights, 0.02), ``scale`` (1.0: the rows
+    are multiplied by it in 32 bits as they enter the stream)."""
 
     def __init__(self, spec: PartSpec, env: BuildEnv):
         super().__init__(spec, env)
         self.vocab = int(spec["vocab"])
         self.hidden = int(spec["hidden"])
         self.init_std = float(spec.get("init_std", 0.02))
+        self.scale = float(spec.get("scale", 1.0))
 
     def param_specs(self) -> Dict[str, ParamSpec]:
         return {"weight": ParamSpec((self.vocab, self.hidden), init=("normal", 0.0, self.init_std))}
 
     def forward(self, token_ids: torch.Tensor, residual: torch.Tensor) -> None:
         ops.embedding_gather(self.params["weight"], token_ids, residual)
+        if self.scale != 1.0:
+            ops.scale_(residual, self.scale)
 
     def table(self) -> torch.Tensor:
         return self.params["weight"]
@@ -49,7 +53,8 @@ class TokenEmbedding(Embedding):
 
 @HEADS.register("linear_head")
 class LinearHead(Head):
-    """params: ``vocab``, ``hidden``, ``tied`` (bool: multiply by the embedding's table), ``scale`` (1.0)."""
+    """params: ``vocab``, ``hidden``, ``tied`` (bool: multiply by the embedding's table), ``scale`` (1.0),
+    ``softcap`` (None or c: the logits become ``c tanh(logits / c)``, after the scale)."""
 
     def __init__(self, spec: PartSpec, env: BuildEnv):
         super().__init__(spec, env)
@@ -57,6 +62,9 @@ class LinearHead(Head):
         self.hidden = int(spec["hidden"])
         self.tied = bool(spec.get("tied", False))
         self.scale = float(spec.get("scale", 1.0))  # logits are multiplied by it
+        self.softcap = None if spec.get("softcap") is None else float(spec["softcap"])
+        if self.softcap is not None and not self.softcap > 0:
+            raise ConfigError("linear_head: a soft cap must be positive")
         self._tied_weight: Optional[torch.Tensor] = None
 
     def param_specs(self) -> Dict[str, ParamSpec]:
@@ -80,6 +88,8 @@ class LinearHead(Head):
             torch.mm(y, w.t(), out=logits, out_dtype=torch.float32)
         if self.scale != 1.0:
             ops.scale_(logits, self.scale)
+        if self.softcap is not None:
+            ops.softcap_(logits, self.softcap)
 
 
 @EMBEDDINGS.register("pass_vectors")

@@ -59,7 +59,7 @@ def split_in_three(w: torch.Tensor) -> Optional[torch.Tensor]:
 class MoE(FeedForward):
     """params: ``hidden``, ``inter``, ``n_experts``, ``top_k``, ``scoring`` ("sigmoid" |
     "softmax"), ``bias`` (bool), ``scale``, ``act``, ``alpha``, ``limit``,
-    ``shared_inter`` (0 = no shared expert), ``router`` ("learned" | "token_table"; the table also needs
+    ``shared_inter`` (0 = no shared expert), ``shared_limit`` (the shared expert's clamp; ``limit`` when absent), ``router`` ("learned" | "token_table"; the table also needs
     ``vocab``).  ``h_f32`` given to the forward calls of a bfloat16 model
     is ``float32(h)``, as a norm's ``out_f32`` is."""
 
@@ -94,7 +94,7 @@ class MoE(FeedForward):
         if self.shared_inter:
             self.shared = GatedMLP(PartSpec("gated_mlp", dict(
                 hidden=self.hidden, inter=self.shared_inter, act=self.act, alpha=self.alpha,
-                limit=self.limit)), env, tag="moe.shared")
+                limit=float(spec.get("shared_limit", self.limit)), init_std=spec.get("init_std"))), env, tag="moe.shared")
 
     def param_specs(self) -> Dict[str, ParamSpec]:
         std = self.spec.get("init_std")  # spread of random expert weights: (into the expert, out of it), default 0.02
@@ -106,9 +106,11 @@ class MoE(FeedForward):
         if self.by_table:
             out["table"] = ParamSpec((self.vocab, self.top_k), "int32", ("distinct_ids", self.n_experts))
         else:
-            out["gate.weight"] = ParamSpec((self.n_experts, self.hidden), "float32")
+            out["gate.weight"] = ParamSpec((self.n_experts, self.hidden), "float32",
+                                           ("normal", 0.0, std_in if std else 0.02))
         if self.has_bias:
-            out["e_score_correction_bias"] = ParamSpec((self.n_experts,), "float32", ("normal", 0.0, 0.01))
+            out["e_score_correction_bias"] = ParamSpec((self.n_experts,), "float32",
+                                                       ("normal", 0.0, 0.5 if std else 0.01))
         return out
 
     def children(self) -> Dict[str, Part]:

@@ -17,7 +17,7 @@ import torch
 
 from ..config.spec import ParamSpec, PartSpec
 from ..kernels import ops
-from .base import NORMS, BuildEnv, Norm, RouteSum, StreamSum
+from .base import NORMS, BuildEnv, Norm, NormedSum, RouteSum, StreamSum
 
 
 @NORMS.register("rmsnorm")
@@ -25,6 +25,7 @@ class RMSNorm(Norm):
     """params: ``size``, ``eps``, ``gemma`` (bool: multiply by ``1 + w``)."""
 
     takes_route_sum = True
+    takes_normed_sum = True
 
     def __init__(self, spec: PartSpec, env: BuildEnv):
         super().__init__(spec, env)
@@ -46,6 +47,11 @@ class RMSNorm(Norm):
         if isinstance(x, StreamSum):
             x.fold(residual)
             x = None
+        if isinstance(x, NormedSum):  # the sub-layer's own norm, the sum and this norm in one pass
+            data, routed = x.kernel_args()
+            ops.postnorm_add_norm(data, routed, x.norm.params["weight"], x.norm.eps, x.norm.gemma, residual,
+                                  self.params["weight"], self.eps, self.gemma, out, out_f32=out_f32, rows=rows)
+            return out
         if isinstance(x, RouteSum):
             ops.add_rmsnorm_routes(x.y, x.pos, x.top_k, x.shared, residual, self.params["weight"], self.eps,
                                    self.gemma, out, out_f32=out_f32, rows=rows)

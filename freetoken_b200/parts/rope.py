@@ -30,7 +30,8 @@ from .base import POSITIONS, BuildEnv, PositionEncoding
 
 @POSITIONS.register("rope_neox")
 class NeoxRope(PositionEncoding):
-    """params: ``rotary_dim`` (even, <= head_dim; 0 disables), ``theta``."""
+    """params: ``rotary_dim`` (even, <= head_dim; 0 disables), ``theta``, ``precise`` (False: the reference's
+    float32 operations; True: angles, cosines and sines in float64, rounded to float32 once)."""
 
     def __init__(self, spec: PartSpec, env: BuildEnv):
         super().__init__(spec, env)
@@ -46,6 +47,11 @@ class NeoxRope(PositionEncoding):
         the cache has been sized)."""
         if self._table is None and self.rotary_dim:
             rd = self.rotary_dim
+            if self.spec.get("precise", False):
+                inv = self.theta ** (-torch.arange(0, rd, 2, dtype=torch.float64) / rd)
+                ang = torch.arange(self.env.max_seq_len, dtype=torch.float64)[:, None] * inv[None, :]
+                self._table = torch.cat((ang.cos(), ang.sin()), dim=-1).float().contiguous().to(self.env.device)
+                return self._table
             inv_freq = 1.0 / (self.theta ** (torch.arange(0, rd, 2, dtype=torch.float) / rd))
             t = torch.arange(self.env.max_seq_len, dtype=torch.float)
             freqs = torch.einsum("i,j -> ij", t, inv_freq)

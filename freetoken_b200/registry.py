@@ -37,6 +37,7 @@ _LAZY: Dict[str, str] = {
     "MiniMaxM3SparseForCausalLM": "freetoken_b200.models.minimax_m3",
     "MiniMaxM3SparseForConditionalGeneration": "freetoken_b200.models.minimax_m3",
     "Rumalorn": "freetoken_b200.models.rumalorn",
+    "Pabavik": "freetoken_b200.models.pabavik",
 }
 
 

@@ -111,7 +111,8 @@ def norm_rope_store(x, head_dim, rotary_dim, positions, rope_table, eps, gemma, 
 
 
 def paged_attention(q, k_slab, v_slab, block_table, seg_info, n_segs, items, n_items, part_o, part_ml,
-                    out, tile_rows, scale, window, sel=None, block_size=0, few_rows=False, dist_bias=None, kv_split=1):
+                    out, tile_rows, scale, window, sel=None, block_size=0, few_rows=False, dist_bias=None, kv_split=1,
+                    sink=None):
     """Per query token, softmax over the visible keys gathered through the block table; the
     work list and the scratch are ignored (they only steer how the kernel splits the work).
     With ``sel`` a query reads only the keys of its chosen blocks."""
@@ -135,7 +136,12 @@ def paged_attention(q, k_slab, v_slab, block_table, seg_info, n_segs, items, n_i
                 if dist_bias is not None:  # [Hq, L] by distance, the last entry for everything farther
                     dist = (p_q - torch.arange(lo, p_q + 1, device=q.device)).clamp(max=dist_bias.shape[1] - 1)
                     s = s + dist_bias.float()[:, dist].view(Hkv, G, -1)
-                p = torch.softmax(s, dim=-1)
+                if sink is None:
+                    p = torch.softmax(s, dim=-1)
+                else:  # a key without a value: it only takes its share of the weights
+                    top = torch.clamp(s.max(dim=-1, keepdim=True).values, min=float(sink))
+                    e = torch.exp(s - top)
+                    p = e / (e.sum(-1, keepdim=True) + torch.exp(float(sink) - top))
                 o = torch.einsum("hgk,khd->hgd", p, vv)
             else:
                 o = torch.zeros(Hkv, G, D, device=q.device)
@@ -187,6 +193,12 @@ def router_topk(logits, bias, top_k, scoring, scale, ids, weights, n_parts=1):
         l = parts[:, 0]
         for q in range(1, n_parts):
             l = l + parts[:, q]
+    if scoring == "softmax_of_chosen":  # the bias belongs to the logit; the softmax runs over the chosen logits only
+        l = l + bias.float() if bias is not None else l
+        idx = torch.argsort(l, dim=-1, descending=True, stable=True)[:, :top_k]
+        ids.copy_(idx.to(torch.int32))
+        weights.copy_(torch.softmax(l.gather(-1, idx), dim=-1) * scale)
+        return
     s = torch.sigmoid(l) if scoring == "sigmoid" else torch.softmax(l, dim=-1)
     c = s + bias.float() if bias is not None else s
     idx = torch.argsort(c, dim=-1, descending=True, stable=True)[:, :top_k]
@@ -352,7 +364,65 @@ def linear(x, w, out, bias=None):
     out.copy_(y.to(out.dtype))
 
 
-ALL = ["stream_add_norm", "head_gate", "table_route", "scale_", "sparse_score_fits", "moe_small_fits", "copy_tokens", "sparse_select", "embedding_gather", "add_rmsnorm", "add_rmsnorm_routes", "act_and_mul", "cast", "table_update", "norm_rope_store",
+def linear_f32(x, w, out):
+    out.copy_(x.float() @ w.float().T)
+
+
+def softcap_(x, cap):
+    x.copy_(cap * torch.tanh(x / cap))
+
+
+def postnorm_add_norm(x, routed, post_weight, post_eps, post_gemma, residual, pre_weight=None, pre_eps=0.0,
+                      pre_gemma=True, out=None, out_f32=None, rows=None):
+    T = residual.shape[0]
+    if routed is not None:
+        pos, top_k, shared = routed
+        a = x.float()[pos.view(-1)[: T * top_k].long()].view(T, top_k, -1).sum(1)
+        if shared is not None:
+            a = a + shared.float()
+    else:
+        a = x.float()[:T]
+    wa = post_weight.float() + 1.0 if post_gemma else post_weight.float()
+    z = residual.float() + a * torch.rsqrt((a * a).mean(-1, keepdim=True) + post_eps) * wa
+    if rows is None:
+        residual.copy_(z)
+    else:
+        z = z[rows.long()]
+    if pre_weight is not None:
+        wr = pre_weight.float() + 1.0 if pre_gemma else pre_weight.float()
+        y = (z * torch.rsqrt((z * z).mean(-1, keepdim=True) + pre_eps) * wr).to(out.dtype)
+        out.view(y.shape).copy_(y)
+        if out_f32 is not None:
+            out_f32.view(y.shape).copy_(y.float())
+
+
+def gated_heads(x, gates, out, dim, act="sigmoid", norm_weight=None, eps=0.0):
+    T, H, _ = x.shape
+    v = x[:, :, :dim].float()
+    if norm_weight is not None:
+        v = v * torch.rsqrt((v * v).mean(-1, keepdim=True) + eps) * norm_weight.float()
+    g = gates.float().view(T, H, dim)
+    s = torch.sigmoid(g)
+    out[:, :, :dim] = (v * (g * s if act == "silu" else s)).to(out.dtype)
+
+
+def gla_scan(q, k, v, z, z_bias, tau, q_scale, state, state_slots, seg_info, n_segs, chunks, n_chunks, seg_chunks,
+             any_single, any_multi, carry, decay_prod, out):
+    """Token by token from each request's slot; the chunk lists only steer how the kernel shares the work."""
+    H, D, Dv = state.shape[1:]
+    zz = z.float() + (z_bias.float().view(1, -1) if z_bias is not None else 0.0)
+    decay = torch.exp(-torch.nn.functional.softplus(-zz) / tau).view(-1, H, D)
+    qq, kk, vv = q.float().view(-1, H, D) * q_scale, k.float().view(-1, H, D), v.float().view(-1, H, Dv)
+    for i, (q_start, q_len, kv_len, _) in enumerate(seg_info.view(-1, 4)[:n_segs].tolist()):
+        slot = int(state_slots[i])
+        S = torch.zeros(H, D, Dv) if kv_len == q_len else state[slot].clone()
+        for t in range(q_start, q_start + q_len):
+            S = decay[t][:, :, None] * S + kk[t][:, :, None] * vv[t][:, None, :]
+            out[t] = torch.einsum("hdv,hd->hv", S, qq[t])
+        state[slot] = S
+
+
+ALL = ["linear_f32", "softcap_", "postnorm_add_norm", "gated_heads", "gla_scan", "stream_add_norm", "head_gate", "table_route", "scale_", "sparse_score_fits", "moe_small_fits", "copy_tokens", "sparse_select", "embedding_gather", "add_rmsnorm", "add_rmsnorm_routes", "act_and_mul", "cast", "table_update", "norm_rope_store",
        "paged_attention", "router_topk", "moe_permute", "moe_route", "moe_route_fits", "linear", "attention_tc_fits", "attention_tc_few_fits", "moe_gemm1_gather_fits", "moe_gather", "moe_gemm1_act", "moe_gemm2",
        "moe_combine", "sample"]
 

@@ -154,8 +154,14 @@ class Engine:
         self.graph_launches: Dict[Any, int] = {}
         # a graph's warm-up runs the step once more, so only mixers whose step can be repeated
         # without changing the result (they say so with ``graph_safe``) may be replayed
+        # (a mixer that keeps a state cannot repeat a step, but its step can still be recorded when everything
+        # it does is decided on the device: it says so with ``graph_recordable``; the step that records then
+        # takes its result from the warm-up run and is not replayed)
+        mixers = self.model.mixers()
         self.use_graphs = (bool(config.cuda_graph) and self.device.type == "cuda"
-                           and all(getattr(m, "graph_safe", False) for m in self.model.mixers()))
+                           and all(getattr(m, "graph_safe", False) or getattr(m, "graph_recordable", False)
+                                   for m in mixers))
+        self.replay_after_record = all(getattr(m, "graph_safe", False) for m in mixers)
         self.steps_run = 0
         self.kernel_launches = 0
 
@@ -345,8 +351,9 @@ class Engine:
         # longest request, which changes the size of the work list a few times over a long decode)
         key = (S, tuple(arr.size for _, arr in builder.sections), tuple(sorted(map(repr, builder.plans))),
                builder.longest_span())
-        if key not in self.graphs:
-            body()  # warm-up: allocates work buffers and library workspaces outside the capture
+        recorded_now = key not in self.graphs
+        if recorded_now:
+            warm = body()  # warm-up: allocates work buffers and library workspaces outside the capture
             torch.cuda.synchronize(self.device)
             graph = torch.cuda.CUDAGraph()
             before = ops.launch_count()
@@ -358,7 +365,12 @@ class Engine:
             self.graph_logits[key] = out
             self.graph_launches[key] = ops.launch_count() - before
         # (after a capture the warm-up has already run this step; the replay repeats it, which
-        # graph_safe mixers allow, so that every result comes from the same code path)
+        # graph_safe mixers allow, so that every result comes from the same code path; with a mixer that keeps
+        # a state the warm-up's result, which lies in the same buffer, is the step's)
+        if recorded_now and not self.replay_after_record:
+            if warm.data_ptr() != self.graph_logits[key].data_ptr():
+                raise SchedulerError("a recorded decode step must leave its logits where the warm-up did")
+            return warm
         self.graphs[key].replay()
         ops.count_launches(self.graph_launches[key])
         return self.graph_logits[key]

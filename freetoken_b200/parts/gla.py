@@ -59,6 +59,7 @@ class GatedLinearAttention(Mixer):
     ``chunk`` (tokens per chunk of a long portion), ``init_std``."""
 
     graph_safe = False  # running a step twice would advance the state twice
+    graph_recordable = True  # but everything a step does is decided on the device: a decode step can be recorded
 
     def __init__(self, spec: PartSpec, env: BuildEnv):
         super().__init__(spec, env)

@@ -172,3 +172,14 @@ def load(folder: str, dtype: torch.dtype = torch.float64):
     weights = {k: (v if v.dtype == torch.int32 else v.to(dtype))
                for k, v in load_file(os.path.join(folder, "model.safetensors")).items()}
     return cfg, weights
+
+
+class PlainPabavik:
+    """A model folder as the tests use one: ``vocab`` and float64 ``logits`` of a whole sequence."""
+
+    def __init__(self, folder: str, dtype: torch.dtype = torch.float64):
+        self.cfg, self.weights = load(folder, dtype)
+        self.vocab = int(self.cfg["vocab"])
+
+    def logits(self, tokens: Sequence[int]) -> torch.Tensor:
+        return forward(self.cfg, self.weights, tokens)

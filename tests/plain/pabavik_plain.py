@@ -14,7 +14,6 @@ file (through the ``safetensors`` package) itself.  Everything is computed in th
 from __future__ import annotations
 
 import json
-import math
 import os
 from typing import Dict, List, Optional, Sequence
 
@@ -112,9 +111,14 @@ def route(h: torch.Tensor, router: torch.Tensor, bias: torch.Tensor, top: int):
     return order, p / p.sum()
 
 
-def expert_mixture(h: torch.Tensor, w: Dict[str, torch.Tensor], f: dict) -> torch.Tensor:
+def expert_mixture(h: torch.Tensor, w: Dict[str, torch.Tensor], f: dict, gaps: Optional[List] = None) -> torch.Tensor:
+    """``gaps`` collects, per token, how far the last chosen expert's logit lies above the best one left out."""
     T = h.shape[0]
     out = torch.zeros(T, w["e0.down"].shape[0], dtype=h.dtype)
+    if gaps is not None:
+        z = torch.sort(h @ w["router"].T + w["router.b"], dim=-1, descending=True).values
+        top = f["router"]["top"]
+        gaps.append(z[:, top - 1] - z[:, top] if top < z.shape[1] else torch.full((T,), float("inf"), dtype=h.dtype))
     for t in range(T):
         ids, ps = route(h[t], w["router"], w["router.b"], f["router"]["top"])
         for e, p in zip(ids, ps):
@@ -134,8 +138,10 @@ def sub(weights: Dict[str, torch.Tensor], prefix: str) -> Dict[str, torch.Tensor
     return {k[len(prefix):]: v for k, v in weights.items() if k.startswith(prefix)}
 
 
-def forward(cfg: dict, weights: Dict[str, torch.Tensor], tokens: Sequence[int], streams: Optional[List] = None) -> torch.Tensor:
-    """Logits ``[T, vocab]`` of one sequence; ``streams`` collects the residual stream after every layer."""
+def forward(cfg: dict, weights: Dict[str, torch.Tensor], tokens: Sequence[int], streams: Optional[List] = None,
+            gaps: Optional[List] = None) -> torch.Tensor:
+    """Logits ``[T, vocab]`` of one sequence; ``streams`` collects the residual stream after every layer,
+    ``gaps`` every router's margins (see :func:`expert_mixture`)."""
     eps = cfg["norm"]["eps"]
     x = weights["embed"][torch.as_tensor(list(tokens))] * cfg["embedding"]["scale"]
     kept = {}
@@ -156,7 +162,7 @@ def forward(cfg: dict, weights: Dict[str, torch.Tensor], tokens: Sequence[int], 
         x = x + rms_norm(a, weights[p + "norm1b"], eps, one_plus=True)
         if layer.get("mlp") is not None:
             h = rms_norm(x, weights[p + "norm2"], eps, one_plus=True)
-            x = x + rms_norm(expert_mixture(h, sub(weights, p + "mlp."), layer["mlp"]), weights[p + "norm2b"], eps,
+            x = x + rms_norm(expert_mixture(h, sub(weights, p + "mlp."), layer["mlp"], gaps), weights[p + "norm2b"], eps,
                              one_plus=True)
         if streams is not None:
             streams.append(x.clone())
@@ -183,3 +189,12 @@ class PlainPabavik:
 
     def logits(self, tokens: Sequence[int]) -> torch.Tensor:
         return forward(self.cfg, self.weights, tokens)
+
+    def router_gaps(self, tokens: Sequence[int]) -> torch.Tensor:
+        """Per token, the smallest margin by which any layer's router made its choice: where it is within the
+        rounding of a bfloat16 run, such a run may choose another expert and its logits differ by more than rounding."""
+        gaps: List[torch.Tensor] = []
+        forward(self.cfg, self.weights, tokens, gaps=gaps)
+        if not gaps:
+            return torch.full((len(tokens),), float("inf"), dtype=torch.float64)
+        return torch.stack(gaps).min(0).values

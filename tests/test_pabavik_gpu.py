@@ -45,12 +45,23 @@ def row_error(got: torch.Tensor, want: torch.Tensor) -> torch.Tensor:
 
 
 F32_ROW, BF16_ROW = 1e-4, 5e-2
+NEAR_TIE = 0.03  # router margins below this are within reach of what a bfloat16 run adds to router logits of order one
 
 
-def assert_rows(got, want, dtype, what=""):
+def assert_rows(got, want, dtype, what="", gaps=None):
+    """``gaps``: the plain model's router margins of the rows.  Where a margin is within bfloat16 rounding a
+    bfloat16 run may choose another expert, which moves that row by more than rounding: such rows (they must be few)
+    are only checked loosely, all others strictly.  32-bit runs are checked strictly everywhere."""
     e = row_error(got.cpu(), want)
-    bound = F32_ROW if dtype == "float32" else BF16_ROW
-    assert torch.isfinite(got).all() and float(e.max()) < bound, f"{what}: worst row {float(e.max()):.3g} at {int(e.argmax())}"
+    assert torch.isfinite(got).all(), what
+    if dtype == "float32" or gaps is None:
+        bound = F32_ROW if dtype == "float32" else BF16_ROW
+        assert float(e.max()) < bound, f"{what}: worst row {float(e.max()):.3g} at {int(e.argmax())}"
+        return
+    sure = gaps[: e.shape[0]] > NEAR_TIE
+    assert float(sure.double().mean()) > 0.6, f"{what}: too many near-ties for a meaningful comparison"
+    assert float(e[sure].max()) < BF16_ROW, f"{what}: worst clear row {float(e[sure].max()):.3g}"
+    assert float(e.max()) < 0.6, f"{what}: worst row {float(e.max()):.3g} at {int(e.argmax())}"
 
 
 # --------------------------------------------------------------------------- norms, gates, cap, router
@@ -363,11 +374,11 @@ def test_cuts_and_batches_agree_with_the_plain_model(name, dtype, tmp_path_facto
     plain = PlainPabavik(folder)
     eng = make_engine(folder, dtype, DEV, PAGE[name], pages=40)
     toks = tokens_for(plain.vocab, 70, 11)
-    want = plain.logits(toks)
-    assert_rows(replay_whole(eng, "w", toks), want, dtype, "whole")
-    assert_rows(replay_cuts(eng, "d", toks, [38]), want, dtype, "last 32 one by one")
-    assert_rows(replay_cuts(eng, "c", toks, [7, 2, 13, 2, 5, 3, 2, 11, 2]), want, dtype, "portions")
-    assert_rows(replay_cuts(eng, "one", toks[:24], []), want[:24], dtype, "one by one from the first token")
+    want, gaps = plain.logits(toks), plain.router_gaps(toks)
+    assert_rows(replay_whole(eng, "w", toks), want, dtype, "whole", gaps)
+    assert_rows(replay_cuts(eng, "d", toks, [38]), want, dtype, "last 32 one by one", gaps)
+    assert_rows(replay_cuts(eng, "c", toks, [7, 2, 13, 2, 5, 3, 2, 11, 2]), want, dtype, "portions", gaps)
+    assert_rows(replay_cuts(eng, "one", toks[:24], []), want[:24], dtype, "one by one from the first token", gaps)
     eng.cache.check()
     eng.check_kernels()
     assert all(g.pool.free_count == g.pool.num_pages for g in eng.cache.paged)
@@ -384,7 +395,7 @@ def test_mixed_steps_with_few_pages_and_slots(name, dtype, tmp_path_factory):
     eng = make_engine(folder, dtype, DEV, P, pages=4 * (-(-64 // P)))
     got = replay_mixed(eng, seqs, mixed_schedule(lengths, seed=3))
     for r, toks in seqs.items():
-        assert_rows(got[r], plain.logits(toks), dtype, r)
+        assert_rows(got[r], plain.logits(toks), dtype, r, plain.router_gaps(toks))
     for g in eng.cache.paged:
         assert g.pool.handed_out > g.pool.num_pages, "the trace was meant to use pages again"
     assert eng.cache.slots.free_count == 4
@@ -397,12 +408,12 @@ def test_long_prompt_long_decoding_and_recorded_steps(dtype, tmp_path_factory):
     folder = model_folder(tmp_path_factory.getbasetemp(), "P1", PABA_1)
     plain = PlainPabavik(folder)
     toks = tokens_for(plain.vocab, 420, 3)
-    want = plain.logits(toks)
+    want, gaps = plain.logits(toks), plain.router_gaps(toks)
     eng = make_engine(folder, dtype, DEV, 16, pages=64, max_step=512)
-    assert_rows(replay_whole(eng, "w", toks), want, dtype, "whole")
-    assert_rows(replay_cuts(eng, "d", toks, [320]), want, dtype, "a hundred tokens one by one")
+    assert_rows(replay_whole(eng, "w", toks), want, dtype, "whole", gaps)
+    assert_rows(replay_cuts(eng, "d", toks, [320]), want, dtype, "a hundred tokens one by one", gaps)
     assert eng.graphs, "the decode steps were meant to be replayed from graphs"
-    assert_rows(replay_cuts(eng, "c", toks, [63, 2, 64, 65, 127, 2, 33] + [1] * 20 + [30, 2]), want, dtype, "portions")
+    assert_rows(replay_cuts(eng, "c", toks, [63, 2, 64, 65, 127, 2, 33] + [1] * 20 + [30, 2]), want, dtype, "portions", gaps)
     other = tokens_for(plain.vocab, 230, 5)
     got = [eng.step([StepEntry("a", toks[:3], [0, 1, 2])]).logits.float().cpu().clone()]
     for i in range(3, 12):
@@ -410,8 +421,8 @@ def test_long_prompt_long_decoding_and_recorded_steps(dtype, tmp_path_factory):
     long = eng.step([StepEntry("b", other, list(range(len(other))))]).logits.float().cpu().clone()
     for i in range(12, 40):
         got.append(eng.step([StepEntry("a", toks[i:i + 1], [0])]).logits.float().cpu().clone())
-    assert_rows(long, plain.logits(other), dtype, "the long step")
-    assert_rows(torch.cat(got), want[:40], dtype, "decode steps before and after it")
+    assert_rows(long, plain.logits(other), dtype, "the long step", plain.router_gaps(other))
+    assert_rows(torch.cat(got), want[:40], dtype, "decode steps before and after it", gaps)
     eng.check_kernels()
 
 
@@ -455,9 +466,10 @@ def test_the_replay_tool_runs_the_design(tmp_path_factory, tmp_path):
         assert [l for l in p.stdout.splitlines() if l.startswith("done")] == ["done 0", "done 1", "done 2"]
         la, lb = plain.logits(a), plain.logits(b)
         got = [np.fromfile(out / f"{i}.f32", dtype="<f4").reshape(-1, plain.vocab) for i in range(3)]
-        assert_rows(torch.from_numpy(got[0]), la[[0, 19]], dtype)
-        assert_rows(torch.from_numpy(got[1]), torch.stack([la[20], lb[8]]), dtype)
-        assert_rows(torch.from_numpy(got[2]), la[[29]], dtype)
+        ga, gb = plain.router_gaps(a), plain.router_gaps(b)
+        assert_rows(torch.from_numpy(got[0]), la[[0, 19]], dtype, "step 0", ga[[0, 19]])
+        assert_rows(torch.from_numpy(got[1]), torch.stack([la[20], lb[8]]), dtype, "step 1", torch.stack([ga[20], gb[8]]))
+        assert_rows(torch.from_numpy(got[2]), la[[29]], dtype, "step 2", ga[[29]])
 
 
 @pytest.mark.parametrize("name,dtype", [("P1", "float32"), ("P4", "bfloat16")])

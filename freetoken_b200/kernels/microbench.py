@@ -9,6 +9,9 @@
     python -m freetoken_b200.kernels.microbench sparse --prefill 2048 --context 32768
     python -m freetoken_b200.kernels.microbench attention --prefill 2048 --tied --dist-bias 200
     python -m freetoken_b200.kernels.microbench rows --tokens 2048 --hidden 3072
+    python -m freetoken_b200.kernels.microbench attention --prefill 2048 --window 1024 --sink
+    python -m freetoken_b200.kernels.microbench gla --prefill 2048 [--heads 16 --dim 128 --vdim 128]
+    python -m freetoken_b200.kernels.microbench gla --batch 8
 
 Each case allocates its inputs once (larger than L2 where the real workload is), warms up, then
 times ``--iters`` launches with CUDA events and prints one JSON line: time, the bytes the kernel has
@@ -136,20 +139,23 @@ def bench_attention(a) -> dict:
     seg = torch.tensor(info, dtype=torch.int32, device=dev)
     q = torch.randn(q0, Hq, D, device=dev, generator=g).to(torch.bfloat16)
     fixed = None
-    tile = 128 if (a.prefill >= 128 and not a.no_tc and ops.attention_tc_fits(D, P, G)) else 64
+    window = int(getattr(a, "window", 0) or 0) or None  # a sliding window: the mma.sync kernels
+    sink = 0.0 if getattr(a, "sink", False) else None  # a sink of logit 0 in the softmax's denominator
+    no_tc = a.no_tc or window is not None or sink is not None
+    tile = 128 if (a.prefill >= 128 and not no_tc and ops.attention_tc_fits(D, P, G)) else 64
     if tile == 128 and a.pair and bias is None:
         tile = 256  # two query tiles per CTA
     few_rows = False
     if not a.prefill:
-        few_rows = a.few_rows and ops.attention_tc_few_fits(D, P, G)
-        tc = few_rows or (a.tc and ops.attention_tc_fits(D, P, G))
+        few_rows = a.few_rows and not no_tc and ops.attention_tc_few_fits(D, P, G)
+        tc = few_rows or (a.tc and not no_tc and ops.attention_tc_fits(D, P, G))
         fixed = wave_splits(len(segs) * Hkv, 148 if tc else 2 * 148, 16, a.context) if a.splits is None else a.splits
         tile = 16 if few_rows else 128 if tc else (16 if G <= 16 else 64)
     tensor_core = few_rows or tile >= 128  # (one CTA per SM: the engine plans these for half as many CTA slots)
     costs = None
     if tile >= 128 and fixed is None:  # as the engine plans these kernels' work lists
         costs = TC_TWO_TILE_COSTS if tile == 256 else TC_ONE_TILE_COSTS
-    plan = build_plan(segs, G, tile, None, Hkv, sm_count=74 if tensor_core else 148, fixed_splits=fixed,
+    plan = build_plan(segs, G, tile, window, Hkv, sm_count=74 if tensor_core else 148, fixed_splits=fixed,
                       key_tile=128 if tensor_core else 0, costs=costs)
     items = torch.from_numpy(plan.items).to(dev)
     po = pm = None
@@ -158,11 +164,14 @@ def bench_attention(a) -> dict:
         pm = torch.empty(plan.n_slots, Hkv, tile, 2, dtype=torch.float32, device=dev)
     out = torch.empty_like(q)
     us = _time(lambda: ops.paged_attention(q, ks, vs, bt, seg, len(segs), items, plan.n_items, po, pm, out, tile,
-                                           D ** -0.5, None, few_rows=few_rows, dist_bias=bias), a.iters, a.warmup,
-               a.profile)
-    kv_bytes = sum(kv for _, kv in segs) * Hkv * D * 2 * (1 if tied else 2)
-    flops = sum(4 * (ql * kv - ql * (ql - 1) // 2) * Hq * D for ql, kv in segs)
-    return {"us": round(us, 2), "tile_rows": tile, "tied": tied, "dist_bias": n_bias, "items": plan.n_items,
+                                           D ** -0.5, window, few_rows=few_rows, dist_bias=bias, sink=sink), a.iters,
+               a.warmup, a.profile)
+    seen = [(ql, kv if window is None else min(kv, window - 1 + ql)) for ql, kv in segs]  # keys a segment's queries can see
+    kv_bytes = sum(kv for _, kv in seen) * Hkv * D * 2 * (1 if tied else 2)
+    pairs = lambda ql, kv: sum(min(kv - ql + t + 1, window or (1 << 60)) for t in range(ql))  # noqa: E731  (query, key) pairs
+    flops = sum(4 * pairs(ql, kv) * Hq * D for ql, kv in segs)
+    return {"us": round(us, 2), "tile_rows": tile, "tied": tied, "dist_bias": n_bias, "window": window, "sink": sink is not None,
+            "items": plan.n_items,
             "est_us": None if plan.est_us is None else round(plan.est_us, 1), "kv_bytes": kv_bytes, "gbs": round(kv_bytes / us / 1e3, 1),
             "hbm_frac": round(kv_bytes / us / 1e3 / HBM_GBS, 3), "tflops": round(flops / us / 1e6, 1),
             "tensor_frac": round(flops / us / 1e6 / BF16_TFLOPS, 3)}
@@ -214,7 +223,58 @@ def bench_rows(a) -> dict:
     o = torch.randn(T, Hq, D, device=dev, generator=g).to(bf)
     gates = torch.randn(T, Hq, device=dev, generator=g).to(bf)
     add("head_gate", lambda: ops.head_gate(o, gates), T * Hq * D * 2 * 2)
+    # a sub-layer's output through a norm of its own into the stream, and the stream's norm, in one pass
+    add("postnorm_add_norm", lambda: ops.postnorm_add_norm(x1, None, w, 1e-6, True, res, w, 1e-6, True, out),
+        T * H * (2 + 4 + 4 + 2))
+    wide = torch.randn(T, Hq * D, device=dev, generator=g).to(bf)
+    add("gated_heads (sigmoid gate, element by element, in place)", lambda: ops.gated_heads(o, wide, o, D, "sigmoid"),
+        T * Hq * D * 2 * 3)
+    o32 = torch.randn(T, Hq, D, device=dev, generator=g)
+    add("gated_heads (32-bit input, head norm, silu gate)", lambda: ops.gated_heads(o32, wide, o, D, "silu", nw, 1e-6),
+        T * Hq * D * (4 + 2 + 2))
     return results
+
+
+def bench_gla(a) -> dict:
+    """The recurrence of gated linear attention: a prompt of --prefill tokens (chunks side by side), or --batch
+    requests with one token each (state in, state out).  Everything is 32-bit arithmetic on the CUDA cores: the
+    figure beside the time is the recurrence's 5 D Dv operations per token and head against the nominal 32-bit
+    rate (148 SMs x 128 lanes x 2 x the SM clock), and the bytes moved against the measured copy rate."""
+    from ..parts.gla import chunk_list
+
+    dev = "cuda"
+    H, D, Dv = a.heads, a.dim, a.vdim
+    segs = [(a.prefill, a.prefill)] if a.prefill else [(1, a.context)] * a.batch
+    T = sum(q for q, _ in segs)
+    g = torch.Generator(device=dev).manual_seed(0)
+    bf = torch.bfloat16
+    wide = (torch.randn(T, 2 * H * D + H * Dv, device=dev, generator=g) * 0.3).to(bf)
+    q, k, v = wide[:, : H * D], wide[:, H * D: 2 * H * D], wide[:, 2 * H * D:]
+    z = torch.randn(T, H * D, device=dev, generator=g) + 2.0
+    zb = torch.zeros(H * D, device=dev)
+    state = torch.zeros(len(segs) + 1, H, D, Dv, device=dev)
+    info, q0 = [], 0
+    for ql, kv in segs:
+        info.append([q0, ql, kv, 0])
+        q0 += ql
+    seg = torch.tensor(info, dtype=torch.int32, device=dev)
+    slots = torch.arange(1, len(segs) + 1, dtype=torch.int32, device=dev)
+    chunks, per_seg, single, multi = chunk_list(segs, a.chunk)
+    n = chunks.shape[0]
+    carry = torch.empty(n, H, D, Dv, device=dev) if multi else None
+    decay = torch.empty(n, H, D, device=dev) if multi else None
+    out = torch.empty(T, H, Dv, device=dev)
+    cd, pd = torch.from_numpy(chunks).to(dev), torch.from_numpy(per_seg).to(dev)
+    us = _time(lambda: ops.gla_scan(q, k, v, z, zb, 16.0, D ** -0.5, state, slots, seg, len(segs), cd, n, pd, single, multi,
+                                    carry, decay, out), a.iters, a.warmup, a.profile)
+    passes = 2 if multi else 1  # a long portion runs the recurrence twice (contributions, then outputs)
+    flops = T * H * D * Dv * (5 if not multi else 8)
+    nbytes = T * (2 * H * D + H * Dv) * 2 * passes + T * H * D * 4 * passes + T * H * Dv * 4 + \
+        (2 * len(segs) + (2 * n if multi else 0)) * H * D * Dv * 4
+    fp32_tflops = 148 * 128 * 2 * 1.965e9 / 1e12
+    return {"us": round(us, 2), "chunks": n, "launches": 4 if multi else 1, "flops": flops, "tflops": round(flops / us / 1e6, 2),
+            "fp32_frac_nominal": round(flops / us / 1e6 / fp32_tflops, 3), "bytes": nbytes,
+            "gbs": round(nbytes / us / 1e3, 1), "hbm_frac": round(nbytes / us / 1e3 / HBM_GBS, 3)}
 
 
 def bench_few(a) -> dict:
@@ -332,7 +392,7 @@ def bench_sample(a) -> dict:
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="microbench")
     sub = ap.add_subparsers(dest="case", required=True)
-    for name in ("moe", "attention", "sample", "sparse", "few", "rows"):
+    for name in ("moe", "attention", "sample", "sparse", "few", "rows", "gla"):
         p = sub.add_parser(name)
         p.add_argument("--iters", type=int, default=20)
         p.add_argument("--warmup", type=int, default=5)
@@ -363,6 +423,8 @@ def main(argv=None) -> int:
             p.add_argument("--pair", action="store_true", help="prefill on the tcgen05 kernel with two query tiles per CTA")
             p.add_argument("--tied", action="store_true", help="the values are the keys (one slab)")
             p.add_argument("--dist-bias", type=int, default=0, help="entries per head of a bias by distance (0 = none)")
+            p.add_argument("--window", type=int, default=0, help="a sliding window of this many tokens (0 = none)")
+            p.add_argument("--sink", action="store_true", help="a sink of logit 0 in the softmax's denominator")
         elif name == "rows":
             p.add_argument("--tokens", type=int, default=2048)
             p.add_argument("--hidden", type=int, default=3072)
@@ -379,6 +441,14 @@ def main(argv=None) -> int:
             p.add_argument("--kv-heads", type=int, default=8)
             p.add_argument("--head-dim", type=int, default=128)
             p.add_argument("--only", choices=["qkv", "out_proj", "gate_up", "down"], default=None)
+        elif name == "gla":
+            p.add_argument("--batch", type=int, default=8)
+            p.add_argument("--context", type=int, default=2048)
+            p.add_argument("--prefill", type=int, default=0)
+            p.add_argument("--heads", type=int, default=16)
+            p.add_argument("--dim", type=int, default=128)
+            p.add_argument("--vdim", type=int, default=128)
+            p.add_argument("--chunk", type=int, default=64)
         elif name == "sparse":
             p.add_argument("--batch", type=int, default=8)
             p.add_argument("--context", type=int, default=32768)
@@ -398,7 +468,7 @@ def main(argv=None) -> int:
             p.add_argument("--temperature", type=float, default=0.0)
     a = ap.parse_args(argv)
     res = {"moe": bench_moe, "attention": bench_attention, "sample": bench_sample, "sparse": bench_sparse, "few": bench_few,
-           "rows": bench_rows}[a.case](a)
+           "rows": bench_rows, "gla": bench_gla}[a.case](a)
     print(json.dumps({"case": a.case, **{k: v for k, v in vars(a).items() if k != "case"}, "result": res}))
     return 0
 

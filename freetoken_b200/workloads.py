@@ -13,7 +13,9 @@ time of a step at the start and at the end of the prompt.
     python bench.py --workload chunked_prefill [--layers 4] [--prompt 131072] [--chunk 512] [--decoders 63]
 
 ``designs``: Rumalorn (parallel Dynamic-Tanh layers, key-tied attention with a bias by distance, experts
-named by a table over token ids) beside MiniMax-M3 at equal layer sizes, both with random weights: a
+named by a table over token ids) and Pabavik (layers normed on both sides of every sub-layer; windowed attention
+with a sink and an output gate, gated linear attention and attention over an earlier layer's cache in turns)
+beside MiniMax-M3 at equal layer sizes, all with random weights: a
 2 048-token prompt in one step and decode steps of eight requests at 2 048 tokens of context, at a few
 sizes that resemble real models' layers.
 
@@ -145,7 +147,24 @@ def _design_configs(width, heads, kv, dim, experts, top, ff, vocab, layers):
           "hidden_act": "silu", "num_local_experts": experts, "num_experts_per_tok": top, "intermediate_size": ff,
           "scoring_func": "sigmoid", "use_routing_bias": True, "routed_scaling_factor": 1.0, "n_shared_experts": 0,
           "torch_dtype": "bfloat16"}
-    return {"rumalorn": ruma, "minimax_m3": m3}
+    # Pabavik: windowed attention with a sink and an output gate, gated linear attention, and attention layers that
+    # read an earlier layer's cache, in turns; the same experts (its router takes the softmax over the chosen logits)
+    window = 1024
+    att = {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "mask": {"size": window},
+           "rot": {"dims": dim // 2, "base": 5000000.0}}
+    gla = {"heads": heads, "dim": dim, "vdim": dim, "tau": 16.0, "decay_rank": 16}
+    pmlp = {"kind": "moe", "expert": {"ff": ff, "limit": 7.0}, "router": {"experts": experts, "top": top}}
+    players = []
+    for i in range(layers):
+        if i % 4 == 0 or (i % 4 == 3):
+            players.append({"type": "attention", "mixer": dict(att), "mlp": pmlp})
+        elif i % 4 == 1:
+            players.append({"type": "gla", "mixer": dict(gla), "mlp": pmlp})
+        else:
+            players.append({"type": "attention", "mixer": dict(att, kv_from=i - 2), "mlp": pmlp})
+    paba = {"architecture": "Pabavik", "vocab": vocab, "width": width, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6},
+            "logit_softcap": 30.0, "layers": players}
+    return {"rumalorn": ruma, "pabavik": paba, "minimax_m3": m3}
 
 
 def _time_design(raw: Dict[str, Any], prompt: int, batch: int, steps: int, warmup: int) -> Dict[str, Any]:
@@ -211,9 +230,10 @@ def designs(raw: Dict[str, Any], layers: int = 4, prompt: int = 2048, batch: int
             row[design] = _time_design(cfg, prompt, batch, steps, warmup)
             gc.collect()
             torch.cuda.empty_cache()
-        row["rumalorn_over_minimax_m3"] = {
-            "prefill": round(row["rumalorn"]["prefill_tokens_per_s"] / row["minimax_m3"]["prefill_tokens_per_s"], 3),
-            "decode": round(row["rumalorn"]["decode_tokens_per_s"] / row["minimax_m3"]["decode_tokens_per_s"], 3)}
+        for design in ("rumalorn", "pabavik"):
+            row[f"{design}_over_minimax_m3"] = {
+                "prefill": round(row[design]["prefill_tokens_per_s"] / row["minimax_m3"]["prefill_tokens_per_s"], 3),
+                "decode": round(row[design]["decode_tokens_per_s"] / row["minimax_m3"]["decode_tokens_per_s"], 3)}
         out["sizes"][name] = row
     return out
 

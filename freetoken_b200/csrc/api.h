@@ -119,9 +119,10 @@ int ftk_gated_heads(const void* x, int x_f32, int x_stride, const void* gates, l
 // requests whose first tokens these are (kv_len == q_len in seg_info).  chunks [n_chunks, 4] = segment, first token
 // within the segment, tokens, place among the segment's chunks (consecutive per segment); seg_chunks [n_segs, 2] =
 // first chunk, chunks.  carry [n_chunks, H, dim, vdim] and decay_prod [n_chunks, H, dim] are scratch for segments
-// of several chunks.  out [T, H, vdim] float32.
+// of several chunks.  out [T, H, vdim] float32.  z [T, H * dim] float32 holds the decay logits and is overwritten
+// (with the decays) when a segment has several chunks.
 int ftk_gla_scan(const void* q, long long q_stride, const void* k, long long k_stride, const void* v,
-                 long long v_stride, int dtype, const float* z, const float* z_bias, float tau, float q_scale,
+                 long long v_stride, int dtype, float* z, const float* z_bias, float tau, float q_scale,
                  float* state, int n_slots, const int32_t* state_slots, const int32_t* seg_info, int n_segs,
                  const int32_t* chunks, int n_chunks, const int32_t* seg_chunks, int any_single, int any_multi,
                  float* carry, float* decay_prod, float* out, int n_tokens, int n_heads, int dim, int vdim,

@@ -16,22 +16,26 @@
 // The recurrence itself is the plain one, token by token, so the result differs from a pure scan only
 // by the rounding of step 2's sums.
 //
-// A block owns 32 value columns of one (chunk, head): 4 warps split the key channels, a thread keeps
-// its share of one state column in registers, and the tokens' q, k and decays are staged in shared
-// memory 32 tokens at a time (float4 reads, the same address for the whole warp).
+// A block owns up to 4 x 32 value columns of one (chunk, head): per group of 32 columns, 4 warps split the key
+// channels, a thread keeps its share of one state column in registers, and the tokens' q, k and decays are
+// staged in shared memory 16 tokens at a time for all of the block's columns (float4 reads, the same address
+// for the whole warp).  Portions of several chunks turn their decay logits into decays once, in place, before
+// the chunks run; a decode step does it while it stages its one token.
 #include "common.cuh"
 
 namespace ftk {
 
-constexpr int kGlaCols = 32;     // value columns per block
-constexpr int kGlaSlices = 4;    // warps per block: each takes a quarter of the key channels
-constexpr int kGlaBatch = 32;    // tokens staged at a time
+constexpr int kGlaCols = 32;     // value columns per group of four warps
+constexpr int kGlaSlices = 4;    // warps per column group: each takes a quarter of the key channels
+constexpr int kGlaBatch = 16;    // tokens staged at a time
+constexpr int kGlaGroups = 4;    // most column groups per block
 
 struct GlaArgs {
   const void* q; const void* k; const void* v;  // rows of the engine's type: token t at + t * stride, head h at + h * dim
   long long q_stride, k_stride, v_stride;
-  const float* z;          // [T, H * D] decay logits (before the bias)
+  float* z;                // [T, H * D] decay logits (before the bias); decays once gla_decay_kernel has run
   const float* z_bias;     // [H * D] or null
+  int z_is_decay;
   float inv_tau, q_scale;
   float* state;            // [slots, H, D, Dv]
   const int32_t* state_slots;  // [S]
@@ -42,7 +46,7 @@ struct GlaArgs {
   float* carry;            // [n_chunks, H, D, Dv]: L_c, then the start state of chunk c + 1
   float* decay_prod;       // [n_chunks, H, D]
   float* out;              // [T, H, Dv]
-  int H, D, Dv, n_tokens;
+  int H, D, Dv, n_tokens, groups;
 };
 
 __device__ __forceinline__ float decay_of(float z, float inv_tau) {
@@ -51,22 +55,31 @@ __device__ __forceinline__ float decay_of(float z, float inv_tau) {
   return expf(-sp * inv_tau);
 }
 
+__global__ void gla_decay_kernel(float* z, const float* __restrict__ bias, long long n, int hd, float inv_tau) {
+  pdl_wait();
+  pdl_trigger();
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) z[i] = decay_of(z[i] + (bias ? bias[i % hd] : 0.f), inv_tau);
+}
+
 // MODE 0: one launch for segments of one chunk (state slot -> outputs -> state slot)
 // MODE 1: local contribution of a chunk from a zero state (no outputs)
 // MODE 3: outputs of a chunk from its start state
 template <typename T, int DPT, int MODE>
-__global__ void __launch_bounds__(kGlaSlices * 32) gla_chunk_kernel(GlaArgs a) {
+__global__ void __launch_bounds__(DPT <= 32 ? kGlaGroups * kGlaSlices * 32 : 2 * kGlaSlices * 32) gla_chunk_kernel(GlaArgs a) {
   pdl_wait();
   pdl_trigger();
-  extern __shared__ float sm[];
+  extern __shared__ __align__(16) float sm[];
   const int D = a.D, Dv = a.Dv;
   const int Dp = DPT * kGlaSlices;              // padded key channels
+  const int cols = a.groups * kGlaCols;         // value columns of this block
   float* sq = sm;                               // [batch][Dp]
   float* sk = sq + kGlaBatch * Dp;
   float* sa = sk + kGlaBatch * Dp;
   float* sv = sa + kGlaBatch * Dp;              // [batch][cols]
-  float* part = sv + kGlaBatch * kGlaCols;      // [slices][batch][cols]
-  const int c = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * kGlaCols;
+  float* part = sv + kGlaBatch * cols;          // [slices][batch][cols]
+  const int c = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * cols;
   const int32_t* ch = a.chunks + (size_t)c * 4;
   const int seg = ch[0], tok0 = ch[1], ntok = ch[2], place = ch[3];
   if (seg < 0 || seg >= a.n_segs || ntok <= 0) return;
@@ -79,8 +92,9 @@ __global__ void __launch_bounds__(kGlaSlices * 32) gla_chunk_kernel(GlaArgs a) {
   if (MODE == 3 && single) return;
   const int slot = a.state_slots[seg];
   if (slot < 0 || slot >= a.n_slots) return;
-  const int slice = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int col = col0 + lane;
+  const int lane = threadIdx.x & 31, slice = (threadIdx.x >> 5) % kGlaSlices, group = threadIdx.x / (kGlaSlices * 32);
+  const int lcol = group * kGlaCols + lane;     // column within the block
+  const int col = col0 + lcol;
   const bool col_ok = col < Dv;
   const int d0 = slice * DPT;
   float s[DPT];
@@ -95,7 +109,7 @@ __global__ void __launch_bounds__(kGlaSlices * 32) gla_chunk_kernel(GlaArgs a) {
   }
 #pragma unroll
   for (int i = 0; i < DPT; ++i) s[i] = (src && col_ok && d0 + i < D) ? src[(size_t)(d0 + i) * Dv + col] : 0.f;
-  float pa[DPT];  // MODE 1: the product of the chunk's decays (the lanes of a warp hold the same values)
+  float pa[MODE == 1 ? DPT : 1];  // MODE 1: the product of the chunk's decays (the lanes of a warp hold the same values)
   if (MODE == 1) {
 #pragma unroll
     for (int i = 0; i < DPT; ++i) pa[i] = 1.f;
@@ -103,33 +117,74 @@ __global__ void __launch_bounds__(kGlaSlices * 32) gla_chunk_kernel(GlaArgs a) {
   const T* qb = (const T*)a.q;
   const T* kb = (const T*)a.k;
   const T* vb = (const T*)a.v;
+  // eight bfloat16 at a time where the rows allow it
+  const bool wide = sizeof(T) == 2 && D % 8 == 0 && a.q_stride % 8 == 0 && a.k_stride % 8 == 0 &&
+                    ((reinterpret_cast<uintptr_t>(a.q) | reinterpret_cast<uintptr_t>(a.k) |
+                      reinterpret_cast<uintptr_t>(a.z)) & 15) == 0;
   for (int b0 = 0; b0 < ntok; b0 += kGlaBatch) {
     const int nb = min(kGlaBatch, ntok - b0);
     __syncthreads();
-    for (int i = threadIdx.x; i < nb * Dp; i += blockDim.x) {
-      const int t = i / Dp, d = i % Dp;
-      const size_t tok = (size_t)(q_start + tok0 + b0 + t);
-      float qv = 0.f, kv = 0.f, av = 1.f;
-      if (d < D) {
-        if (MODE != 1) qv = to_float(qb[tok * a.q_stride + (size_t)h * D + d]) * a.q_scale;
-        kv = to_float(kb[tok * a.k_stride + (size_t)h * D + d]);
-        const float z = a.z[(tok * a.H + h) * D + d] + (a.z_bias ? a.z_bias[(size_t)h * D + d] : 0.f);
-        av = decay_of(z, a.inv_tau);
+    if (wide) {
+      const int per_row = Dp / 8;
+      for (int i = threadIdx.x; i < nb * per_row; i += blockDim.x) {
+        const int t = i / per_row, d = (i % per_row) * 8;
+        const size_t tok = (size_t)(q_start + tok0 + b0 + t);
+        float qv[8], kv[8], av[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) { qv[u] = 0.f; kv[u] = 0.f; av[u] = 1.f; }
+        if (d < D) {
+          const uint4 kr = *reinterpret_cast<const uint4*>(kb + tok * a.k_stride + (size_t)h * D + d);
+          const __nv_bfloat162* k2 = reinterpret_cast<const __nv_bfloat162*>(&kr);
+#pragma unroll
+          for (int u = 0; u < 4; ++u) { const float2 f = __bfloat1622float2(k2[u]); kv[2 * u] = f.x; kv[2 * u + 1] = f.y; }
+          if (MODE != 1) {
+            const uint4 qr = *reinterpret_cast<const uint4*>(qb + tok * a.q_stride + (size_t)h * D + d);
+            const __nv_bfloat162* q2 = reinterpret_cast<const __nv_bfloat162*>(&qr);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) { const float2 f = __bfloat1622float2(q2[u]); qv[2 * u] = f.x * a.q_scale; qv[2 * u + 1] = f.y * a.q_scale; }
+          }
+          const float* zr = a.z + (tok * a.H + h) * D + d;
+          const float4 z0 = *reinterpret_cast<const float4*>(zr), z1 = *reinterpret_cast<const float4*>(zr + 4);
+          av[0] = z0.x; av[1] = z0.y; av[2] = z0.z; av[3] = z0.w; av[4] = z1.x; av[5] = z1.y; av[6] = z1.z; av[7] = z1.w;
+          if (!a.z_is_decay) {
+#pragma unroll
+            for (int u = 0; u < 8; ++u) av[u] = decay_of(av[u] + (a.z_bias ? a.z_bias[(size_t)h * D + d + u] : 0.f), a.inv_tau);
+          }
+        }
+        float* dq = sq + t * Dp + d; float* dk = sk + t * Dp + d; float* da = sa + t * Dp + d;
+        *reinterpret_cast<float4*>(dq) = make_float4(qv[0], qv[1], qv[2], qv[3]);
+        *reinterpret_cast<float4*>(dq + 4) = make_float4(qv[4], qv[5], qv[6], qv[7]);
+        *reinterpret_cast<float4*>(dk) = make_float4(kv[0], kv[1], kv[2], kv[3]);
+        *reinterpret_cast<float4*>(dk + 4) = make_float4(kv[4], kv[5], kv[6], kv[7]);
+        *reinterpret_cast<float4*>(da) = make_float4(av[0], av[1], av[2], av[3]);
+        *reinterpret_cast<float4*>(da + 4) = make_float4(av[4], av[5], av[6], av[7]);
       }
-      sq[i] = qv; sk[i] = kv; sa[i] = av;
+    } else {
+      for (int i = threadIdx.x; i < nb * Dp; i += blockDim.x) {
+        const int t = i / Dp, d = i % Dp;
+        const size_t tok = (size_t)(q_start + tok0 + b0 + t);
+        float qv = 0.f, kv = 0.f, av = 1.f;
+        if (d < D) {
+          if (MODE != 1) qv = to_float(qb[tok * a.q_stride + (size_t)h * D + d]) * a.q_scale;
+          kv = to_float(kb[tok * a.k_stride + (size_t)h * D + d]);
+          av = a.z[(tok * a.H + h) * D + d];
+          if (!a.z_is_decay) av = decay_of(av + (a.z_bias ? a.z_bias[(size_t)h * D + d] : 0.f), a.inv_tau);
+        }
+        sq[i] = qv; sk[i] = kv; sa[i] = av;
+      }
     }
-    for (int i = threadIdx.x; i < nb * kGlaCols; i += blockDim.x) {
-      const int t = i / kGlaCols, j = i % kGlaCols;
+    for (int i = threadIdx.x; i < nb * cols; i += blockDim.x) {
+      const int t = i / cols, j = i % cols;
       const size_t tok = (size_t)(q_start + tok0 + b0 + t);
       sv[i] = col0 + j < Dv ? to_float(vb[tok * a.v_stride + (size_t)h * Dv + col0 + j]) : 0.f;
     }
     __syncthreads();
     for (int t = 0; t < nb; ++t) {
-      const float vj = sv[t * kGlaCols + lane];
+      const float vj = sv[t * cols + lcol];
       const float4* q4 = reinterpret_cast<const float4*>(sq + t * Dp + d0);
       const float4* k4 = reinterpret_cast<const float4*>(sk + t * Dp + d0);
       const float4* a4 = reinterpret_cast<const float4*>(sa + t * Dp + d0);
-      float acc = 0.f;
+      float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;  // four chains, added in a fixed order
 #pragma unroll
       for (int i = 0; i < DPT / 4; ++i) {
         const float4 av = a4[i], kv = k4[i];
@@ -141,22 +196,22 @@ __global__ void __launch_bounds__(kGlaSlices * 32) gla_chunk_kernel(GlaArgs a) {
           pa[4 * i + 0] *= av.x; pa[4 * i + 1] *= av.y; pa[4 * i + 2] *= av.z; pa[4 * i + 3] *= av.w;
         } else {
           const float4 qv = q4[i];
-          acc = fmaf(s[4 * i + 0], qv.x, acc);
-          acc = fmaf(s[4 * i + 1], qv.y, acc);
-          acc = fmaf(s[4 * i + 2], qv.z, acc);
-          acc = fmaf(s[4 * i + 3], qv.w, acc);
+          acc0 = fmaf(s[4 * i + 0], qv.x, acc0);
+          acc1 = fmaf(s[4 * i + 1], qv.y, acc1);
+          acc2 = fmaf(s[4 * i + 2], qv.z, acc2);
+          acc3 = fmaf(s[4 * i + 3], qv.w, acc3);
         }
       }
-      if (MODE != 1) part[(slice * kGlaBatch + t) * kGlaCols + lane] = acc;
+      if (MODE != 1) part[(slice * kGlaBatch + t) * cols + lcol] = (acc0 + acc1) + (acc2 + acc3);
     }
     if (MODE != 1) {
       __syncthreads();
-      for (int i = threadIdx.x; i < nb * kGlaCols; i += blockDim.x) {
-        const int t = i / kGlaCols, j = i % kGlaCols;
+      for (int i = threadIdx.x; i < nb * cols; i += blockDim.x) {
+        const int t = i / cols, j = i % cols;
         if (col0 + j < Dv) {
           float o = 0.f;
 #pragma unroll
-          for (int w = 0; w < kGlaSlices; ++w) o += part[(w * kGlaBatch + t) * kGlaCols + j];  // slices in order
+          for (int w = 0; w < kGlaSlices; ++w) o += part[(w * kGlaBatch + t) * cols + j];  // slices in order
           a.out[((size_t)(q_start + tok0 + b0 + t) * a.H + h) * Dv + col0 + j] = o;
         }
       }
@@ -171,7 +226,7 @@ __global__ void __launch_bounds__(kGlaSlices * 32) gla_chunk_kernel(GlaArgs a) {
     for (int i = 0; i < DPT; ++i)
       if (d0 + i < D) dst[(size_t)(d0 + i) * Dv + col] = s[i];
   }
-  if (MODE == 1 && blockIdx.z == 0 && lane == 0) {
+  if (MODE == 1 && blockIdx.z == 0 && group == 0 && lane == 0) {
 #pragma unroll
     for (int i = 0; i < DPT; ++i)
       if (d0 + i < D) a.decay_prod[((size_t)c * a.H + h) * D + d0 + i] = pa[i];
@@ -202,11 +257,15 @@ __global__ void gla_carry_kernel(GlaArgs a) {
 }
 
 template <typename T, int DPT>
-static int launch_gla(const GlaArgs& a, bool any_single, bool any_multi, cudaStream_t s) {
+static int launch_gla(GlaArgs a, bool any_single, bool any_multi, cudaStream_t s) {
   const int Dp = DPT * kGlaSlices;
-  const size_t smem = ((size_t)3 * kGlaBatch * Dp + kGlaBatch * kGlaCols + (size_t)kGlaSlices * kGlaBatch * kGlaCols) *
+  const int tiles = (a.Dv + kGlaCols - 1) / kGlaCols;
+  a.groups = min(tiles, DPT <= 32 ? kGlaGroups : 2);
+  const int cols = a.groups * kGlaCols;
+  const int threads = a.groups * kGlaSlices * 32;
+  const size_t smem = ((size_t)3 * kGlaBatch * Dp + (size_t)kGlaBatch * cols + (size_t)kGlaSlices * kGlaBatch * cols) *
                       sizeof(float);
-  dim3 grid(a.n_chunks, a.H, (a.Dv + kGlaCols - 1) / kGlaCols);
+  dim3 grid(a.n_chunks, a.H, (a.Dv + cols - 1) / cols);
   auto k0 = gla_chunk_kernel<T, DPT, 0>;
   auto k1 = gla_chunk_kernel<T, DPT, 1>;
   auto k3 = gla_chunk_kernel<T, DPT, 3>;
@@ -215,18 +274,25 @@ static int launch_gla(const GlaArgs& a, bool any_single, bool any_multi, cudaStr
     cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     cudaFuncSetAttribute(k3, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   }
+  if (any_multi) {  // the decays of all of the step's tokens, once, where the logits lay
+    const long long n = (long long)a.n_tokens * a.H * a.D;
+    const unsigned blocks = (unsigned)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+    FTK_LAUNCH(gla_decay_kernel, blocks, 256, 0, s, a.z, a.z_bias, n, a.H * a.D, a.inv_tau);
+    FTK_LAUNCH_CHECK("gla_scan (decays)");
+    a.z_is_decay = 1;
+  }
   if (any_single) {
-    FTK_LAUNCH(k0, grid, kGlaSlices * 32, smem, s, a);
+    FTK_LAUNCH(k0, grid, threads, smem, s, a);
     FTK_LAUNCH_CHECK("gla_scan (one chunk per request)");
   }
   if (any_multi) {
-    FTK_LAUNCH(k1, grid, kGlaSlices * 32, smem, s, a);
+    FTK_LAUNCH(k1, grid, threads, smem, s, a);
     FTK_LAUNCH_CHECK("gla_scan (chunk contributions)");
     const size_t DV = (size_t)a.D * a.Dv;
     dim3 cgrid((unsigned)((DV + 255) / 256), a.n_segs, a.H);
     FTK_LAUNCH(gla_carry_kernel, cgrid, 256, 0, s, a);
     FTK_LAUNCH_CHECK("gla_scan (carry)");
-    FTK_LAUNCH(k3, grid, kGlaSlices * 32, smem, s, a);
+    FTK_LAUNCH(k3, grid, threads, smem, s, a);
     FTK_LAUNCH_CHECK("gla_scan (chunk outputs)");
   }
   return 0;
@@ -237,7 +303,7 @@ static int launch_gla(const GlaArgs& a, bool any_single, bool any_multi, cudaStr
 using namespace ftk;
 
 extern "C" int ftk_gla_scan(const void* q, long long q_stride, const void* k, long long k_stride, const void* v,
-                            long long v_stride, int dtype, const float* z, const float* z_bias, float tau,
+                            long long v_stride, int dtype, float* z, const float* z_bias, float tau,
                             float q_scale, float* state, int n_slots, const int32_t* state_slots,
                             const int32_t* seg_info, int n_segs, const int32_t* chunks, int n_chunks,
                             const int32_t* seg_chunks, int any_single, int any_multi, float* carry,
@@ -256,7 +322,7 @@ extern "C" int ftk_gla_scan(const void* q, long long q_stride, const void* k, lo
   FTK_REQUIRE(!any_multi || (carry && decay_prod), "gla_scan: portions of several chunks need scratch");
   GlaArgs a;
   a.q = q; a.k = k; a.v = v; a.q_stride = q_stride; a.k_stride = k_stride; a.v_stride = v_stride;
-  a.z = z; a.z_bias = z_bias; a.inv_tau = 1.f / tau; a.q_scale = q_scale;
+  a.z = z; a.z_bias = z_bias; a.z_is_decay = 0; a.groups = 1; a.inv_tau = 1.f / tau; a.q_scale = q_scale;
   a.state = state; a.state_slots = state_slots; a.seg_info = seg_info; a.chunks = chunks; a.seg_chunks = seg_chunks;
   a.n_chunks = n_chunks; a.n_segs = n_segs; a.n_slots = n_slots; a.carry = carry; a.decay_prod = decay_prod;
   a.out = out; a.H = n_heads; a.D = dim; a.Dv = vdim; a.n_tokens = n_tokens;

@@ -30,52 +30,97 @@ struct SandwichArgs {
   int post_gemma, pre_gemma;
 };
 
-template <typename T>
+// One block per row.  Everything the row needs from memory (the sub-layer's output, the stream, both weights) is
+// asked for in the first pass, four elements a thread at a time where the row allows it; the second and third
+// pass work from shared memory and registers.  `arow` holds a * w_a, `zrow` the stream's row, then the sum.
+template <typename T, bool VEC>
 __global__ void __launch_bounds__(256) postnorm_add_norm_kernel(SandwichArgs a) {
   pdl_wait();
   pdl_trigger();
-  extern __shared__ float zrow[];
+  extern __shared__ __align__(16) float srow[];
   __shared__ float red[33];
+  float* arow = srow;
+  float* zrow = srow + a.hidden;
   const int r = blockIdx.x;
   const int src_row = a.rows ? a.rows[r] : r;
   const size_t src = (size_t)src_row * a.hidden, dst = (size_t)r * a.hidden;
   const T* x = (const T*)a.x;
   const T* shared = (const T*)a.shared;
+  constexpr int W = VEC ? 4 : 1;
   float ss = 0.f;
-  for (int i = threadIdx.x; i < a.hidden; i += blockDim.x) {
-    float v;
+  for (int i = threadIdx.x * W; i < a.hidden; i += blockDim.x * W) {
+    float v[4], res[4], wa[4];
+    if constexpr (VEC) {
+      Vec4<float>::load(a.residual + src + i, res);
+      Vec4<float>::load(a.post_w + i, wa);
+    } else {
+      res[0] = a.residual[src + i];
+      wa[0] = a.post_w[i];
+    }
     if (a.route_pos) {
-      v = 0.f;
+#pragma unroll
+      for (int u = 0; u < W; ++u) v[u] = 0.f;
       for (int j = 0; j < a.top_k; ++j) {  // route order
         const int p = a.route_pos[(size_t)src_row * a.top_k + j];
-        if (p >= 0 && p < a.n_routes) v += to_float(x[(size_t)p * a.hidden + i]);
+        if (p >= 0 && p < a.n_routes) {
+          float y[4];
+          if constexpr (VEC) Vec4<T>::load(x + (size_t)p * a.hidden + i, y);
+          else y[0] = to_float(x[(size_t)p * a.hidden + i]);
+#pragma unroll
+          for (int u = 0; u < W; ++u) v[u] += y[u];
+        }
       }
-      if (shared) v += to_float(shared[src + i]);
+      if (shared) {
+        float y[4];
+        if constexpr (VEC) Vec4<T>::load(shared + src + i, y);
+        else y[0] = to_float(shared[src + i]);
+#pragma unroll
+        for (int u = 0; u < W; ++u) v[u] += y[u];
+      }
     } else {
-      v = to_float(x[src + i]);
+      if constexpr (VEC) Vec4<T>::load(x + src + i, v);
+      else v[0] = to_float(x[src + i]);
     }
-    zrow[i] = v;
-    ss += v * v;
+#pragma unroll
+    for (int u = 0; u < W; ++u) {
+      ss += v[u] * v[u];
+      arow[i + u] = v[u] * (a.post_gemma ? 1.f + wa[u] : wa[u]);
+      zrow[i + u] = res[u];
+    }
   }
   ss = block_sum(ss, red);
   const float inv_a = rsqrtf(ss / (float)a.hidden + a.post_eps);
   float ss2 = 0.f;
-  for (int i = threadIdx.x; i < a.hidden; i += blockDim.x) {
-    const float w = a.post_gemma ? 1.f + a.post_w[i] : a.post_w[i];
-    const float z = a.residual[src + i] + zrow[i] * inv_a * w;
-    if (!a.rows) a.residual[src + i] = z;
-    zrow[i] = z;
-    ss2 += z * z;
+  for (int i = threadIdx.x * W; i < a.hidden; i += blockDim.x * W) {
+    float z[4];
+#pragma unroll
+    for (int u = 0; u < W; ++u) {
+      z[u] = zrow[i + u] + arow[i + u] * inv_a;
+      zrow[i + u] = z[u];
+      ss2 += z[u] * z[u];
+    }
+    if (!a.rows) {
+      if constexpr (VEC) Vec4<float>::store(a.residual + src + i, z);
+      else a.residual[src + i] = z[0];
+    }
   }
   if (!a.pre_w) return;
   ss2 = block_sum(ss2, red);
   const float inv_r = rsqrtf(ss2 / (float)a.hidden + a.pre_eps);
   T* out = (T*)a.out;
-  for (int i = threadIdx.x; i < a.hidden; i += blockDim.x) {
-    const float w = a.pre_gemma ? 1.f + a.pre_w[i] : a.pre_w[i];
-    const T y = from_float<T>(zrow[i] * inv_r * w);
-    if (out) out[dst + i] = y;
-    if (a.out_f32) a.out_f32[dst + i] = to_float(y);
+  for (int i = threadIdx.x * W; i < a.hidden; i += blockDim.x * W) {
+    float wr[4], y[4];
+    if constexpr (VEC) Vec4<float>::load(a.pre_w + i, wr);
+    else wr[0] = a.pre_w[i];
+#pragma unroll
+    for (int u = 0; u < W; ++u) y[u] = to_float(from_float<T>(zrow[i + u] * inv_r * (a.pre_gemma ? 1.f + wr[u] : wr[u])));
+    if constexpr (VEC) {
+      if (out) Vec4<T>::store(out + dst + i, y);
+      if (a.out_f32) Vec4<float>::store(a.out_f32 + dst + i, y);
+    } else {
+      if (out) out[dst + i] = from_float<T>(y[0]);
+      if (a.out_f32) a.out_f32[dst + i] = y[0];
+    }
   }
 }
 
@@ -144,16 +189,21 @@ extern "C" int ftk_postnorm_add_norm(const void* x, int dtype, const int32_t* ro
   a.post_w = post_w; a.residual = residual; a.pre_w = pre_w; a.out = out; a.out_f32 = out_f32; a.rows = rows;
   a.n_rows = n_rows; a.hidden = hidden; a.post_eps = post_eps; a.pre_eps = pre_eps;
   a.post_gemma = post_gemma; a.pre_gemma = pre_gemma;
-  const size_t smem = (size_t)hidden * sizeof(float);
+  const size_t smem = (size_t)2 * hidden * sizeof(float);
   FTK_REQUIRE(smem <= 200 * 1024, "postnorm_add_norm: rows of %d elements do not fit shared memory", hidden);
+  auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  const bool vec = hidden % 8 == 0 && al16(x) && al16(shared) && al16(residual) && al16(post_w) && al16(pre_w) &&
+                   al16(out) && al16(out_f32);
+  auto go = [&](auto kern) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return FTK_LAUNCH(kern, n_rows, 256, smem, stream, a);
+  };
   if (dtype == FTK_F32) {
-    auto kern = postnorm_add_norm_kernel<float>;
-    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    FTK_LAUNCH(kern, n_rows, 256, smem, stream, a);
+    if (vec) go(postnorm_add_norm_kernel<float, true>);
+    else go(postnorm_add_norm_kernel<float, false>);
   } else {
-    auto kern = postnorm_add_norm_kernel<__nv_bfloat16>;
-    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    FTK_LAUNCH(kern, n_rows, 256, smem, stream, a);
+    if (vec) go(postnorm_add_norm_kernel<__nv_bfloat16, true>);
+    else go(postnorm_add_norm_kernel<__nv_bfloat16, false>);
   }
   FTK_LAUNCH_CHECK("postnorm_add_norm");
   return 0;

@@ -1043,7 +1043,7 @@ def gla_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor,
     ``S <- diag(a_t) S + k_t v_t^T``, ``o_t = S^T (q_t q_scale)``, ``a_t = sigmoid(z_t + z_bias)^(1 / tau)``.
 
     ``q, k [T, H * D]`` and ``v [T, H * Dv]`` of the engine's dtype (views of adjacent columns of a wider
-    tensor are fine); ``z [T, H * D]`` float32; ``state [slots, H, D, Dv]`` float32, read from and left in
+    tensor are fine); ``z [T, H * D]`` float32 (overwritten with the decays when a segment has several chunks); ``state [slots, H, D, Dv]`` float32, read from and left in
     the slot ``state_slots[segment]`` (a segment with ``kv_len == q_len`` starts from zero);
     ``chunks [n, 4]`` / ``seg_chunks [S, 2]`` from :func:`freetoken_b200.parts.gla.chunk_list`; ``carry
     [n, H, D, Dv]`` and ``decay_prod [n, H, D]`` float32 scratch for segments of several chunks;
@@ -1062,7 +1062,7 @@ def gla_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor,
         raise KernelError("gla_scan: scratch for segments of several chunks is missing or too small")
     if chunks.numel() < 4 * n_chunks or seg_chunks.numel() < 2 * n_segs:
         raise KernelError("gla_scan: chunk lists too short")
-    launches = (1 if any_single else 0) + (3 if any_multi else 0)
+    launches = (1 if any_single else 0) + (4 if any_multi else 0)
     _check(_lib().ftk_gla_scan(
         q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), _code(q, "q"),
         _dev(z, "z", torch.float32), _dev(z_bias, "z_bias", torch.float32), float(tau), float(q_scale),

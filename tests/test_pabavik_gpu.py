@@ -308,7 +308,7 @@ def run_gla(dtype, H, D, Dv, segs, chunk, tau=4.0, problem=None, n_slots=6):
     decay = torch.full((n, H, D), float("nan"), device=DEV) if multi else None
     out, want = torch.full((T, H, Dv), float("nan"), device=DEV), torch.zeros(T, H, Dv)
     s_got, s_want = state.clone(), state.clone().cpu()
-    ops.gla_scan(q, k, v, z, zb, tau, D ** -0.5, s_got, slots, seg_info, len(segs), torch.from_numpy(chunks).to(DEV), n,
+    ops.gla_scan(q, k, v, z.clone(), zb, tau, D ** -0.5, s_got, slots, seg_info, len(segs), torch.from_numpy(chunks).to(DEV), n,
                  torch.from_numpy(per_seg).to(DEV), single, multi, carry, decay, out)
     ref.gla_scan(q.cpu(), k.cpu(), v.cpu(), z.cpu(), zb.cpu(), tau, D ** -0.5, s_want, slots.cpu(), seg_info.cpu(), len(segs),
                  None, n, None, single, multi, None, None, want)
@@ -341,7 +341,7 @@ def test_gla_cut_anywhere_gives_the_same_outputs_and_state(dtype):
             chunks, per_seg, single, multi = chunk_list([(n, done + n)], 64)
             m = chunks.shape[0]
             o = torch.empty(n, H, Dv, device=DEV)
-            ops.gla_scan(q[done:done + n], k[done:done + n], v[done:done + n], z[done:done + n].contiguous(), zb, 4.0,
+            ops.gla_scan(q[done:done + n], k[done:done + n], v[done:done + n], z[done:done + n].clone(), zb, 4.0,
                          D ** -0.5, st, slots, seg, 1, torch.from_numpy(chunks).to(DEV), m, torch.from_numpy(per_seg).to(DEV),
                          single, multi, torch.empty(m, H, D, Dv, device=DEV), torch.empty(m, H, D, device=DEV), o)
             outs.append(o.cpu())

@@ -16,19 +16,23 @@
 // The recurrence itself is the plain one, token by token, so the result differs from a pure scan only
 // by the rounding of step 2's sums.
 //
-// A block owns up to 4 x 32 value columns of one (chunk, head): per group of 32 columns, 4 warps split the key
-// channels, a thread keeps its share of one state column in registers, and the tokens' q, k and decays are
-// staged in shared memory 16 tokens at a time for all of the block's columns (float4 reads, the same address
-// for the whole warp).  Portions of several chunks turn their decay logits into decays once, in place, before
+// A block owns 64 (or 32) value columns of one (chunk, head): per group of that many columns, 4 warps split the
+// key channels, a thread keeps its share of two (or one) state columns in registers, and the tokens' q, k and
+// decays are staged in shared memory 16 tokens at a time for all of the block's columns (float4 reads, the same
+// address for the whole warp).  Portions of several chunks turn their decay logits into decays once, in place, before
 // the chunks run; a decode step does it while it stages its one token.
 #include "common.cuh"
 
 namespace ftk {
 
-constexpr int kGlaCols = 32;     // value columns per group of four warps
 constexpr int kGlaSlices = 4;    // warps per column group: each takes a quarter of the key channels
 constexpr int kGlaBatch = 16;    // tokens staged at a time
-constexpr int kGlaGroups = 4;    // most column groups per block
+// value columns per thread: two (columns lane and lane + 32 of the group's 64) while a thread's share of the key
+// channels leaves the registers for it; every q, k and decay read from shared memory then serves two columns
+__host__ __device__ constexpr int gla_cols_per_thread(int dpt) { return dpt <= 32 ? 2 : 1; }
+// column groups (of four warps) per block: one (measured on B200 at 16 heads of 128 x 128, 2,048 tokens: 276 us
+// against 306 with two groups, whose 256 threads of 150 to 170 registers leave an SM a single block)
+__host__ __device__ constexpr int gla_max_groups(int dpt) { return 1; }
 
 struct GlaArgs {
   const void* q; const void* k; const void* v;  // rows of the engine's type: token t at + t * stride, head h at + h * dim
@@ -67,12 +71,14 @@ __global__ void gla_decay_kernel(float* z, const float* __restrict__ bias, long 
 // MODE 1: local contribution of a chunk from a zero state (no outputs)
 // MODE 3: outputs of a chunk from its start state
 template <typename T, int DPT, int MODE>
-__global__ void __launch_bounds__(DPT <= 32 ? kGlaGroups * kGlaSlices * 32 : 2 * kGlaSlices * 32) gla_chunk_kernel(GlaArgs a) {
+__global__ void __launch_bounds__(gla_max_groups(DPT) * kGlaSlices * 32) gla_chunk_kernel(GlaArgs a) {
   pdl_wait();
   pdl_trigger();
   extern __shared__ __align__(16) float sm[];
   const int D = a.D, Dv = a.Dv;
   const int Dp = DPT * kGlaSlices;              // padded key channels
+  constexpr int NC = gla_cols_per_thread(DPT);
+  constexpr int kGlaCols = 32 * NC;             // value columns per group of four warps
   const int cols = a.groups * kGlaCols;         // value columns of this block
   float* sq = sm;                               // [batch][Dp]
   float* sk = sq + kGlaBatch * Dp;
@@ -93,11 +99,10 @@ __global__ void __launch_bounds__(DPT <= 32 ? kGlaGroups * kGlaSlices * 32 : 2 *
   const int slot = a.state_slots[seg];
   if (slot < 0 || slot >= a.n_slots) return;
   const int lane = threadIdx.x & 31, slice = (threadIdx.x >> 5) % kGlaSlices, group = threadIdx.x / (kGlaSlices * 32);
-  const int lcol = group * kGlaCols + lane;     // column within the block
+  const int lcol = group * kGlaCols + lane;     // the thread's first column within the block (the second: + 32)
   const int col = col0 + lcol;
-  const bool col_ok = col < Dv;
   const int d0 = slice * DPT;
-  float s[DPT];
+  float s[NC][DPT];
   // the start state
   const bool fresh = kv_len - q_len == 0;
   const float* src = nullptr;
@@ -108,7 +113,10 @@ __global__ void __launch_bounds__(DPT <= 32 ? kGlaGroups * kGlaSlices * 32 : 2 *
     src = a.carry + ((size_t)from * a.H + h) * D * Dv;
   }
 #pragma unroll
-  for (int i = 0; i < DPT; ++i) s[i] = (src && col_ok && d0 + i < D) ? src[(size_t)(d0 + i) * Dv + col] : 0.f;
+  for (int n = 0; n < NC; ++n)
+#pragma unroll
+    for (int i = 0; i < DPT; ++i)
+      s[n][i] = (src && col + 32 * n < Dv && d0 + i < D) ? src[(size_t)(d0 + i) * Dv + col + 32 * n] : 0.f;
   float pa[MODE == 1 ? DPT : 1];  // MODE 1: the product of the chunk's decays (the lanes of a warp hold the same values)
   if (MODE == 1) {
 #pragma unroll
@@ -180,29 +188,42 @@ __global__ void __launch_bounds__(DPT <= 32 ? kGlaGroups * kGlaSlices * 32 : 2 *
     }
     __syncthreads();
     for (int t = 0; t < nb; ++t) {
-      const float vj = sv[t * cols + lcol];
+      float vj[NC], acc[NC][4];  // four chains per column, added in a fixed order
+#pragma unroll
+      for (int n = 0; n < NC; ++n) {
+        vj[n] = sv[t * cols + lcol + 32 * n];
+        acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+      }
       const float4* q4 = reinterpret_cast<const float4*>(sq + t * Dp + d0);
       const float4* k4 = reinterpret_cast<const float4*>(sk + t * Dp + d0);
       const float4* a4 = reinterpret_cast<const float4*>(sa + t * Dp + d0);
-      float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;  // four chains, added in a fixed order
 #pragma unroll
       for (int i = 0; i < DPT / 4; ++i) {
         const float4 av = a4[i], kv = k4[i];
-        s[4 * i + 0] = fmaf(av.x, s[4 * i + 0], kv.x * vj);
-        s[4 * i + 1] = fmaf(av.y, s[4 * i + 1], kv.y * vj);
-        s[4 * i + 2] = fmaf(av.z, s[4 * i + 2], kv.z * vj);
-        s[4 * i + 3] = fmaf(av.w, s[4 * i + 3], kv.w * vj);
+        float4 qv = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (MODE != 1) qv = q4[i];
+#pragma unroll
+        for (int n = 0; n < NC; ++n) {
+          s[n][4 * i + 0] = fmaf(av.x, s[n][4 * i + 0], kv.x * vj[n]);
+          s[n][4 * i + 1] = fmaf(av.y, s[n][4 * i + 1], kv.y * vj[n]);
+          s[n][4 * i + 2] = fmaf(av.z, s[n][4 * i + 2], kv.z * vj[n]);
+          s[n][4 * i + 3] = fmaf(av.w, s[n][4 * i + 3], kv.w * vj[n]);
+          if (MODE != 1) {
+            acc[n][0] = fmaf(s[n][4 * i + 0], qv.x, acc[n][0]);
+            acc[n][1] = fmaf(s[n][4 * i + 1], qv.y, acc[n][1]);
+            acc[n][2] = fmaf(s[n][4 * i + 2], qv.z, acc[n][2]);
+            acc[n][3] = fmaf(s[n][4 * i + 3], qv.w, acc[n][3]);
+          }
+        }
         if (MODE == 1) {
           pa[4 * i + 0] *= av.x; pa[4 * i + 1] *= av.y; pa[4 * i + 2] *= av.z; pa[4 * i + 3] *= av.w;
-        } else {
-          const float4 qv = q4[i];
-          acc0 = fmaf(s[4 * i + 0], qv.x, acc0);
-          acc1 = fmaf(s[4 * i + 1], qv.y, acc1);
-          acc2 = fmaf(s[4 * i + 2], qv.z, acc2);
-          acc3 = fmaf(s[4 * i + 3], qv.w, acc3);
         }
       }
-      if (MODE != 1) part[(slice * kGlaBatch + t) * cols + lcol] = (acc0 + acc1) + (acc2 + acc3);
+      if (MODE != 1) {
+#pragma unroll
+        for (int n = 0; n < NC; ++n)
+          part[(slice * kGlaBatch + t) * cols + lcol + 32 * n] = (acc[n][0] + acc[n][1]) + (acc[n][2] + acc[n][3]);
+      }
     }
     if (MODE != 1) {
       __syncthreads();
@@ -221,10 +242,12 @@ __global__ void __launch_bounds__(DPT <= 32 ? kGlaGroups * kGlaSlices * 32 : 2 *
   float* dst = nullptr;
   if (MODE == 0 || (MODE == 3 && last)) dst = a.state + ((size_t)slot * a.H + h) * D * Dv;
   if (MODE == 1) dst = a.carry + ((size_t)c * a.H + h) * D * Dv;
-  if (dst && col_ok) {
+  if (dst) {
 #pragma unroll
-    for (int i = 0; i < DPT; ++i)
-      if (d0 + i < D) dst[(size_t)(d0 + i) * Dv + col] = s[i];
+    for (int n = 0; n < NC; ++n)
+#pragma unroll
+      for (int i = 0; i < DPT; ++i)
+        if (d0 + i < D && col + 32 * n < Dv) dst[(size_t)(d0 + i) * Dv + col + 32 * n] = s[n][i];
   }
   if (MODE == 1 && blockIdx.z == 0 && group == 0 && lane == 0) {
 #pragma unroll
@@ -259,8 +282,9 @@ __global__ void gla_carry_kernel(GlaArgs a) {
 template <typename T, int DPT>
 static int launch_gla(GlaArgs a, bool any_single, bool any_multi, cudaStream_t s) {
   const int Dp = DPT * kGlaSlices;
+  constexpr int kGlaCols = 32 * gla_cols_per_thread(DPT);
   const int tiles = (a.Dv + kGlaCols - 1) / kGlaCols;
-  a.groups = min(tiles, DPT <= 32 ? kGlaGroups : 2);
+  a.groups = min(tiles, gla_max_groups(DPT));
   const int cols = a.groups * kGlaCols;
   const int threads = a.groups * kGlaSlices * 32;
   const size_t smem = ((size_t)3 * kGlaBatch * Dp + (size_t)kGlaBatch * cols + (size_t)kGlaSlices * kGlaBatch * cols) *
@@ -312,7 +336,7 @@ extern "C" int ftk_gla_scan(const void* q, long long q_stride, const void* k, lo
   FTK_REQUIRE(dtype_ok(dtype), "gla_scan: bad dtype %d", dtype);
   FTK_REQUIRE(n_tokens >= 0 && n_segs >= 0 && n_chunks >= 0, "gla_scan: bad counts");
   if (n_tokens == 0 || n_chunks == 0) return 0;
-  FTK_REQUIRE(n_heads >= 1 && n_heads <= 65535 && dim >= 1 && dim <= 256 && vdim >= 1 && vdim <= 65535 * kGlaCols,
+  FTK_REQUIRE(n_heads >= 1 && n_heads <= 65535 && dim >= 1 && dim <= 256 && vdim >= 1 && vdim <= 65535 * 32,
               "gla_scan: %d heads of %d key and %d value channels are not taken (at most 256 key channels)", n_heads,
               dim, vdim);
   FTK_REQUIRE(n_segs <= 65535, "gla_scan: too many segments");

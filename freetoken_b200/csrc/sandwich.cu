@@ -124,6 +124,92 @@ __global__ void __launch_bounds__(256) postnorm_add_norm_kernel(SandwichArgs a) 
   }
 }
 
+// The same for rows of at most 1,024 x PER elements that allow 16-byte accesses: a thread keeps its (at most PER x 4)
+// elements of a w_a and of the stream in registers, so the three passes touch neither shared memory (but for the two
+// sums over the block) nor, after the first, global memory; the stream norm's weight is asked for in the first pass too.
+template <typename T, int PER>
+__global__ void __launch_bounds__(256) postnorm_add_norm_regs_kernel(SandwichArgs a) {
+  pdl_wait();
+  pdl_trigger();
+  __shared__ float red[33];
+  const int r = blockIdx.x;
+  const int src_row = a.rows ? a.rows[r] : r;
+  const size_t src = (size_t)src_row * a.hidden, dst = (size_t)r * a.hidden;
+  const T* x = (const T*)a.x;
+  const T* shared = (const T*)a.shared;
+  float av[PER][4], zv[PER][4], wr[PER][4];
+  int route[8];
+  if (a.route_pos) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) route[j] = j < a.top_k ? a.route_pos[(size_t)src_row * a.top_k + j] : -1;
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int p = 0; p < PER; ++p) {
+    const int i = (p * 256 + threadIdx.x) * 4;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) av[p][u] = zv[p][u] = wr[p][u] = 0.f;
+    if (i >= a.hidden) continue;
+    float v[4], wa[4];
+    Vec4<float>::load(a.residual + src + i, zv[p]);
+    Vec4<float>::load(a.post_w + i, wa);
+    if (a.pre_w) Vec4<float>::load(a.pre_w + i, wr[p]);
+    if (a.route_pos) {
+      v[0] = v[1] = v[2] = v[3] = 0.f;
+      for (int j = 0; j < a.top_k; ++j) {  // route order
+        const int q = j < 8 ? route[j] : a.route_pos[(size_t)src_row * a.top_k + j];
+        if (q >= 0 && q < a.n_routes) {
+          float y[4];
+          Vec4<T>::load(x + (size_t)q * a.hidden + i, y);
+#pragma unroll
+          for (int u = 0; u < 4; ++u) v[u] += y[u];
+        }
+      }
+      if (shared) {
+        float y[4];
+        Vec4<T>::load(shared + src + i, y);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) v[u] += y[u];
+      }
+    } else {
+      Vec4<T>::load(x + src + i, v);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      ss += v[u] * v[u];
+      av[p][u] = v[u] * (a.post_gemma ? 1.f + wa[u] : wa[u]);
+    }
+  }
+  ss = block_sum(ss, red);
+  const float inv_a = rsqrtf(ss / (float)a.hidden + a.post_eps);
+  float ss2 = 0.f;
+#pragma unroll
+  for (int p = 0; p < PER; ++p) {
+    const int i = (p * 256 + threadIdx.x) * 4;
+    if (i >= a.hidden) continue;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      zv[p][u] += av[p][u] * inv_a;
+      ss2 += zv[p][u] * zv[p][u];
+    }
+    if (!a.rows) Vec4<float>::store(a.residual + src + i, zv[p]);
+  }
+  if (!a.pre_w) return;
+  ss2 = block_sum(ss2, red);
+  const float inv_r = rsqrtf(ss2 / (float)a.hidden + a.pre_eps);
+  T* out = (T*)a.out;
+#pragma unroll
+  for (int p = 0; p < PER; ++p) {
+    const int i = (p * 256 + threadIdx.x) * 4;
+    if (i >= a.hidden) continue;
+    float y[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) y[u] = to_float(from_float<T>(zv[p][u] * inv_r * (a.pre_gemma ? 1.f + wr[p][u] : wr[p][u])));
+    if (out) Vec4<T>::store(out + dst + i, y);
+    if (a.out_f32) Vec4<float>::store(a.out_f32 + dst + i, y);
+  }
+}
+
 // One warp per (token, head).  x: [T, n_heads, x_stride] (XT), g: row t at g + t * g_stride, head h at + h * dim,
 // out: [T, n_heads, out_stride] (T).  Columns past `dim` of a padded destination are left as they are.
 template <typename XT, typename T>
@@ -198,7 +284,21 @@ extern "C" int ftk_postnorm_add_norm(const void* x, int dtype, const int32_t* ro
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     return FTK_LAUNCH(kern, n_rows, 256, smem, stream, a);
   };
-  if (dtype == FTK_F32) {
+  const int per = (hidden + 1023) / 1024;  // 16-byte pieces a thread of 256 holds of a row
+  if (vec && per <= 8) {  // the row stays in registers
+    const int P = per <= 1 ? 1 : per <= 2 ? 2 : per <= 4 ? 4 : 8;
+    if (dtype == FTK_F32) {
+      if (P == 1) FTK_LAUNCH((postnorm_add_norm_regs_kernel<float, 1>), n_rows, 256, 0, stream, a);
+      else if (P == 2) FTK_LAUNCH((postnorm_add_norm_regs_kernel<float, 2>), n_rows, 256, 0, stream, a);
+      else if (P == 4) FTK_LAUNCH((postnorm_add_norm_regs_kernel<float, 4>), n_rows, 256, 0, stream, a);
+      else FTK_LAUNCH((postnorm_add_norm_regs_kernel<float, 8>), n_rows, 256, 0, stream, a);
+    } else {
+      if (P == 1) FTK_LAUNCH((postnorm_add_norm_regs_kernel<__nv_bfloat16, 1>), n_rows, 256, 0, stream, a);
+      else if (P == 2) FTK_LAUNCH((postnorm_add_norm_regs_kernel<__nv_bfloat16, 2>), n_rows, 256, 0, stream, a);
+      else if (P == 4) FTK_LAUNCH((postnorm_add_norm_regs_kernel<__nv_bfloat16, 4>), n_rows, 256, 0, stream, a);
+      else FTK_LAUNCH((postnorm_add_norm_regs_kernel<__nv_bfloat16, 8>), n_rows, 256, 0, stream, a);
+    }
+  } else if (dtype == FTK_F32) {
     if (vec) go(postnorm_add_norm_kernel<float, true>);
     else go(postnorm_add_norm_kernel<float, false>);
   } else {

@@ -72,7 +72,7 @@ typedef struct {
   // heads); 0 or 1 = as given.  Not with the tcgen05 kernels.
   int kv_split;
   // a sink in the softmax's denominator: weight_j = e^(s_j) / (e^sink_logit + sum_i e^(s_i)); the sink has no value.
-  // Not with the tcgen05 kernels, nor with block selection.
+  // Of the tcgen05 kernels the one with 128-row tiles takes it; not with block selection.
   int has_sink;
   float sink_logit;
 } FtkAttnExtras;

@@ -998,7 +998,9 @@ static int paged_attention_tc_impl(const void* q, const void* k_slab, const void
               "paged_attention_tc: tiles of 16 rows take at most 16 heads per KV head, got %d", n_q_heads / n_kv_heads);
   FTK_REQUIRE(n_tokens >= 1 && n_items >= 0 && n_segs >= 1 && num_pages >= 1 && bt_stride >= 1,
               "paged_attention_tc: bad sizes");
-  FTK_REQUIRE(window == 0, "paged_attention_tc: layers with a window run on the other kernels");
+  FTK_REQUIRE(window == 0 || (form == kTcSingle && k_slab != v_slab && !(extras && extras->dist_bias)),
+              "paged_attention_tc: of the tcgen05 kernels the one with 128-row tiles takes a window (values of their own, no "
+              "distance bias)");
   FTK_REQUIRE(n_slots == 0 || (part_o && part_ml), "paged_attention_tc: split tiles need scratch");
   FTK_REQUIRE((((uintptr_t)q | (uintptr_t)k_slab | (uintptr_t)v_slab | (uintptr_t)out) & 15) == 0,
               "paged_attention_tc: 16-byte aligned tensors only");
@@ -1015,11 +1017,14 @@ static int paged_attention_tc_impl(const void* q, const void* k_slab, const void
   p.dist_len = extras ? extras->dist_len : 0;
   p.slab_heads = n_kv_heads; p.kv_split = 1;
   FTK_REQUIRE(!extras || extras->kv_split <= 1, "paged_attention_tc: KV heads are not split for the tcgen05 kernels");
-  p.has_sink = 0; p.sink = 0.f;
-  FTK_REQUIRE(!extras || !extras->has_sink, "paged_attention_tc: a softmax sink runs on the other kernels");
+  p.has_sink = extras ? extras->has_sink : 0;
+  p.sink = extras ? extras->sink_logit : 0.f;
+  FTK_REQUIRE(!p.has_sink || (form == kTcSingle && !p.dist_bias),
+              "paged_attention_tc: of the tcgen05 kernels the one with 128-row tiles takes a softmax sink");
   cudaStream_t s = (cudaStream_t)stream;
   if (p.dist_bias) note_variant(few ? "attention: tcgen05, tiles of at most 16 rows, bias by distance"
                                     : "attention: tcgen05, 128-row query tiles, bias by distance");
+  else if (window > 0 || p.has_sink) note_variant("attention: tcgen05, 128-row query tiles, window or sink");
   else
   note_variant(pair ? "attention: tcgen05, two 128-row query tiles per CTA"
                : few ? "attention: tcgen05, tiles of at most 16 rows, one softmax warp"

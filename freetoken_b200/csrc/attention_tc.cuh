@@ -584,6 +584,19 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           }
           const int key0 = it.kb + i * kTcKeys;
           const int live = it.ke - key0;  // keys of the request in this tile
+          if (p.window > 0) {
+            // a windowed piece starts at a multiple of the key tile at or before the first key that its first row
+            // sees: the value rows before that key are zeroed too (their pages may have gone back to the pool)
+            const int dead = min(kTcKeys, max(0, it.kv_len - it.q_len + it.tok0 - p.window + 1) - key0);
+            if (dead > 0) {
+              for (int x = lane; x < dead * 16; x += 32) {
+                const int r = x / 16, h = (x / 8) & 1, c = x & 7;
+                *reinterpret_cast<uint4*>(tiles + (v_tile0 + vs) * kTcTile + h * kTcHalf + r * 128 + c * 16) =
+                    make_uint4(0u, 0u, 0u, 0u);
+              }
+              fence_async_smem();
+            }
+          }
           if (live < kTcKeys) {
             // the value rows past the end of the request: zero, whatever the page holds there (the rest of
             // the last loaded box) and whatever the stage held before (boxes that were not loaded)
@@ -637,6 +650,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     const int qpos = r < R ? pos_base + r / G : -1;
     // last key this row may read; rows past the tile's last are never stored and must not hold the others up
     const int hi = r < R ? min(it.ke - 1, qpos) : 0x7fffffff;
+    // first key the row may read (a sliding window); rows that the tile does not have need no mask
+    const int lo = (p.window > 0 && r < R) ? qpos - p.window + 1 : 0;
     // a learned bias by distance (see AttnParams::dist_bias): the row of this thread's head, and the factor that
     // turns a bias into raw-score units (the scores are scaled after the maximum is taken)
     const float* brow = (BIASED && r < R) ? p.dist_bias + (size_t)(kvh * G + r % G) * p.dist_len : nullptr;
@@ -663,14 +678,14 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_empty[sb]);  // the next product may overwrite this buffer
       // a tile that every row of the warp reads in full needs no mask (most tiles of a long prompt)
-      const bool interior = __all_sync(0xffffffffu, key0 + kTcKeys - 1 <= hi);
+      const bool interior = __all_sync(0xffffffffu, key0 + kTcKeys - 1 <= hi && key0 >= lo);
       if (!interior) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          if (key0 + i > hi) v0[i] = -INFINITY;
-          if (key0 + 32 + i > hi) v1[i] = -INFINITY;
-          if (key0 + 64 + i > hi) v2[i] = -INFINITY;
-          if (key0 + 96 + i > hi) v3[i] = -INFINITY;
+          if (key0 + i > hi || key0 + i < lo) v0[i] = -INFINITY;
+          if (key0 + 32 + i > hi || key0 + 32 + i < lo) v1[i] = -INFINITY;
+          if (key0 + 64 + i > hi || key0 + 64 + i < lo) v2[i] = -INFINITY;
+          if (key0 + 96 + i > hi || key0 + 96 + i < lo) v3[i] = -INFINITY;
         }
       }
       float tile_bias = 0.f;  // what every score of this tile and row gets added, in the exp2 domain
@@ -765,7 +780,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       const bool live = n_tiles > 0;
       const int tok = it.q_start + it.tok0 + r / G;
       if (it.nsplit == 1) {
-        const float inv = l > 0.f ? 1.f / l : 0.f;
+        // (a sink in the denominator: e^sink relative to the running maximum, which is in the exp2 domain)
+        const float lt = l + (p.has_sink ? exp2f(p.sink * 1.4426950408889634f - m_used) : 0.f);
+        const float inv = lt > 0.f ? 1.f / lt : 0.f;
         __nv_bfloat16* dst = (__nv_bfloat16*)p.out + ((size_t)tok * p.Hq + kvh * G + r % G) * kTcD;
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {

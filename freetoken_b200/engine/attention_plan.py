@@ -159,6 +159,8 @@ def build_plan(segments: Sequence[Tuple[int, int]], group: int, tile_rows: int,
     lo = np.zeros_like(hi)
     if window is not None:
         lo = np.maximum(0, pos0 + tok0 - window + 1)
+        if key_tile:  # these kernels fetch whole boxes of keys: a piece starts on a key tile, the kernel masks the rest
+            lo = lo // key_tile * key_tile
     if sparse:
         block, topk = sparse
         lo = np.zeros_like(hi)

@@ -446,7 +446,8 @@ def paged_attention(q: torch.Tensor, k_slab: torch.Tensor, v_slab: torch.Tensor,
 
     ``sink`` (a logit, or None): the softmax's denominator also holds ``e^sink``, a key without a value, so a
     row's weights are ``e^(s_j) / (e^sink + sum_i e^(s_i))``.  A tile that is split along the keys gets it once,
-    in the merge.  Not with the tcgen05 kernels, nor with block selection.
+    in the merge.  Not with block selection.  Of the tcgen05 kernels the one with 128-row tiles takes a window and a
+    sink (its work list then starts every piece on a key tile: ``build_plan(..., window, key_tile=128)``).
     """
     T, Hq, D = q.shape
     pages, Hkv, P, D2 = k_slab.shape
@@ -466,8 +467,23 @@ def paged_attention(q: torch.Tensor, k_slab: torch.Tensor, v_slab: torch.Tensor,
         raise KernelError(f"paged_attention: few_rows goes with tiles of 16 rows, got {tile_rows}")
     if tile_rows in (128, 256) or few_rows:
         # bfloat16 steps on the tcgen05 kernels: one query tile per CTA, a pair of them, or tiles of a few rows
-        if sel is not None or window or q.dtype != torch.bfloat16 or sink is not None:
-            raise KernelError("paged_attention: the tcgen05 kernels take bfloat16 without window, sink or block selection")
+        if sel is not None or q.dtype != torch.bfloat16:
+            raise KernelError("paged_attention: the tcgen05 kernels take bfloat16 without block selection")
+        if window or sink is not None:  # the form with one 128-row query tile a piece takes both
+            if tile_rows != 128 or few_rows or dist_bias is not None or v_slab.data_ptr() == k_slab.data_ptr():
+                raise KernelError("paged_attention: of the tcgen05 kernels the one with 128-row tiles takes a window or a "
+                                  "sink (values of their own, no distance bias)")
+            ex = _AttnExtras(None, 0, 1, 0 if sink is None else 1, 0.0 if sink is None else float(sink))
+            _check(_lib().ftk_paged_attention_tc_ex(
+                _dev(q, "q"), _dev(k_slab, "k_slab"), _dev(v_slab, "v_slab"),
+                _dev(block_table, "block_table", torch.int32), block_table.shape[1],
+                _dev(seg_info, "seg_info", torch.int32), n_segs,
+                _dev(items, "items", torch.int32), n_items,
+                _dev(part_o, "part_o", torch.float32), _dev(part_ml, "part_ml", torch.float32), n_slots,
+                _dev(out, "out"), T, Hq, Hkv, D, P, pages, float(scale), int(window) if window else 0, ctypes.byref(ex),
+                0, _stream()),
+                "paged_attention (tcgen05, window or sink)", 2 if n_slots else 1)
+            return
         if dist_bias is not None:  # the forms with one query tile a piece (128 rows, or at most 16) take it
             if tile_rows == 256 or dist_bias.dim() != 2 or dist_bias.shape[0] != Hq:
                 raise KernelError("paged_attention: of the tcgen05 kernels the ones with one query tile a piece take a "

@@ -42,7 +42,7 @@ TC_MIN_DECODE_SPAN = 0   # decode steps go there from this length of the longest
 
 def attention_kernel_form(dtype: torch.dtype, decode_only: bool = False, group: int = 1, n_tokens: int = 0,
                           head_dim: int = 0, page_size: int = 0, window: Optional[int] = None,
-                          longest_span: int = 0, one_tile_only: bool = False) -> Tuple[int, bool]:
+                          longest_span: int = 0, one_tile_only: bool = False, no_few: bool = False) -> Tuple[int, bool]:
     """``(query rows one attention CTA handles, the tcgen05 kernel's form for few rows)``.
 
     16 rows in the 32-bit kernel.  bfloat16 steps whose sizes the tcgen05 kernels take: 128 rows for
@@ -55,12 +55,15 @@ def attention_kernel_form(dtype: torch.dtype, decode_only: bool = False, group: 
     request's length rounded up to a power of two, from which on they go there:
     ``TC_MIN_DECODE_SPAN``), larger groups to the 128-row kernel.  Otherwise 16 rows for decode steps
     of small groups and 64 in the bfloat16 mma.sync kernels.  ``one_tile_only``: of the tcgen05 kernels only
-    the ones with a single query tile a piece may be chosen (they are the ones that take a bias by distance)."""
+    the ones with a single query tile a piece may be chosen (they are the ones that take a bias by distance);
+    ``no_few``: nor the form for tiles of at most 16 rows (a window or a sink: the 128-row form alone takes them)."""
     if dtype != torch.bfloat16:
         return 16, False
-    sized = bool(window is None and head_dim and page_size)
+    sized = bool(head_dim and page_size)
+    if window is not None:  # (of the tcgen05 kernels the one with a single 128-row tile a piece takes a window)
+        one_tile_only = no_few = True
     if decode_only:
-        if sized and longest_span >= TC_MIN_DECODE_SPAN:
+        if sized and not no_few and longest_span >= TC_MIN_DECODE_SPAN:
             if ops.attention_tc_few_fits(head_dim, page_size, group):
                 return 16, True
             if ops.attention_tc_fits(head_dim, page_size, group):
@@ -186,10 +189,12 @@ class GQAttention(Mixer):
 
     # ------------------------------------------------------------------ step
     def kernel_form(self, decode_only: bool, n_tokens: int = 0, page_size: int = 0, longest_span: int = 0):
-        # (the tcgen05 kernels take neither a sink nor split KV heads)
-        sized = self.sink is None and self.kv_split == 1
+        # (the tcgen05 kernels take no split KV heads; a sink or a window goes with the 128-row form alone)
+        sized = self.kv_split == 1
+        special = self.sink is not None or self.window is not None
         return attention_kernel_form(self.env.dtype, decode_only, self.plan_group, n_tokens,
-                                     self.pad_dim if sized else 0, page_size, self.window, longest_span)
+                                     self.pad_dim if sized else 0, page_size, self.window, longest_span,
+                                     one_tile_only=special, no_few=special)
 
     def tile_rows(self, decode_only: bool, n_tokens: int = 0, page_size: int = 0, longest_span: int = 0) -> int:
         return self.kernel_form(decode_only, n_tokens, page_size, longest_span)[0]
@@ -205,7 +210,7 @@ class GQAttention(Mixer):
         # forward() of the same step runs the kernel this work list was made for
         rows, few_rows = self.kernel_form(builder.decode_only, n_tokens, page_size, builder.longest_span())
         if rows >= 128 and not few_rows and not builder.decode_only and n_tokens >= TC_PAIR_MIN_TOKENS_LONG \
-                and hasattr(builder, "cheaper_attention_rows"):
+                and self.sink is None and self.window is None and hasattr(builder, "cheaper_attention_rows"):
             # one or two query tiles a piece: whichever work list the kernel is estimated to get through sooner
             rows = builder.cheaper_attention_rows(self.plan_group, self.window, self.plan_kv_heads, self.pad_dim)
         self._step_plan = builder.attention_plan(self.plan_group, rows, self.window, self.plan_kv_heads, self.pad_dim,

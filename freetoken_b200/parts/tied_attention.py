@@ -145,7 +145,8 @@ class TiedKVAttention(Mixer):
     def kernel_form(self, decode_only: bool, n_tokens: int = 0, page_size: int = 0, longest_span: int = 0):
         # (of the tcgen05 kernels the ones with a single query tile a piece take a bias by distance)
         return attention_kernel_form(self.env.dtype, decode_only, self.plan_group, n_tokens,
-                                     self.pad_dim if self.kv_split == 1 else 0, page_size, self.window, longest_span,
+                                     self.pad_dim if self.kv_split == 1 and self.window is None else 0, page_size,
+                                     self.window, longest_span,
                                      one_tile_only=True)
 
     def plan_key(self, decode_only: bool = False, n_tokens: int = 0, page_size: int = 0, longest_span: int = 0):

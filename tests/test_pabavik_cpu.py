@@ -137,7 +137,7 @@ def test_the_plain_router_takes_the_softmax_over_the_chosen_logits_only():
 
 
 # --------------------------------------------------------------------------- the engine on the CPU
-@pytest.mark.parametrize("name", ["P1", "P2", "P3", "P4", "P5"])
+@pytest.mark.parametrize("name", ["P1", "P2", "P3", "P4", "P5", "P6"])
 def test_cuts_and_batches_agree_with_the_plain_model(name, cpu_ops, tmp_path_factory):
     folder = model_folder(tmp_path_factory.getbasetemp(), name, ALL[name])
     plain = PlainPabavik(folder)

@@ -179,6 +179,8 @@ def run_attention(dtype, Hq, Hkv, D, P, segs, tile, window, sink, fixed_splits=N
                   kv_split=1, scale=None):
     q, ks, vs, bt, seg = problem or attention_problem(dtype, Hq, Hkv, D, P, segs)
     kw = dict(sm_count=4096, min_split_keys=32) if force_split else dict(sm_count=148)
+    if tile == 128:
+        kw["key_tile"] = 128  # as the engine plans the tcgen05 kernel's work
     Hv = Hkv * kv_split
     plan = build_plan(segs, Hq // Hv, tile, window, Hv, fixed_splits=fixed_splits, **kw)
     items = torch.from_numpy(plan.items).to(DEV)
@@ -219,6 +221,32 @@ def test_attention_with_sink_and_window(dtype, Hq, Hkv, D, P, window):
     # without a sink nothing changed
     out, want, _ = run_attention(dtype, Hq, Hkv, D, P, segs, tile, window, None)
     torch.testing.assert_close(out.float(), want.float(), **attn_tol(dtype))
+
+
+@pytest.mark.parametrize("Hq,Hkv,P,window", [(12, 2, 16, 200), (4, 4, 32, 37), (16, 1, 16, 128), (6, 2, 64, 1), (8, 2, 16, 1000),
+                                               (6, 2, 16, None)])
+def test_window_and_sink_on_the_tensor_core_kernel(Hq, Hkv, P, window):
+    """The tcgen05 kernel with 128-row tiles: pieces that start on a key tile before the window's first key, pages
+    before the window that hold NaN (they may have gone back to the pool), tiles split along the keys."""
+    dtype = torch.bfloat16
+    for segs, force in (([(300, 300)], False), ([(128, 128), (1, 40), (200, 517), (3, 3)], False), ([(256, 900)], True),
+                        ([(130, 1000)], False)):
+        for sink in (0.0, None, 2.0):
+            if window is None and sink is None:
+                continue
+            problem = attention_problem(dtype, Hq, Hkv, 128, P, segs, seed=6)
+            q, ks, vs, bt, seg = problem
+            if window is not None:  # what no query of the step can see any more: NaN, as a page given back may hold
+                for q_start, q_len, kv_len, row in seg.tolist():
+                    for j in range(0, max(0, kv_len - q_len - window + 1)):
+                        ks[int(bt[row, j // P]), :, j % P] = float("nan")
+                        vs[int(bt[row, j // P]), :, j % P] = float("nan")
+            ops.variant_counts(reset=True)
+            out, want, plan = run_attention(dtype, Hq, Hkv, 128, P, segs, 128, window, sink, force_split=force, problem=problem)
+            assert ops.variant_counts().get("attention: tcgen05, 128-row query tiles, window or sink", 0) == 1
+            assert not force or window is not None or plan.n_slots > 0
+            torch.testing.assert_close(out.float(), want.float(), **attn_tol(dtype))
+    assert ops.read_status() == 0
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -407,6 +435,28 @@ def test_mixed_steps_with_few_pages_and_slots(name, dtype, tmp_path_factory):
     for g in eng.cache.paged:
         assert g.pool.handed_out > g.pool.num_pages, "the trace was meant to use pages again"
     assert eng.cache.slots.free_count == 4
+
+
+def test_long_steps_of_heads_of_128_run_the_tensor_core_attention(tmp_path_factory):
+    folder = model_folder(tmp_path_factory.getbasetemp(), "P6", ALL["P6"])
+    plain = PlainPabavik(folder)
+    toks = tokens_for(plain.vocab, 450, 9)
+    want, gaps = plain.logits(toks), plain.router_gaps(toks)
+    eng = make_engine(folder, "bfloat16", DEV, 16, pages=96, max_step=512)
+    ops.variant_counts(reset=True)
+    assert_rows(replay_whole(eng, "w", toks), want, "bfloat16", "whole", gaps)
+    assert ops.variant_counts().get("attention: tcgen05, 128-row query tiles, window or sink", 0) == 3
+    assert_rows(replay_cuts(eng, "c", toks, [200, 130, 2, 100]), want, "bfloat16", "portions, the rest one by one", gaps)
+    others = {f"o{i}": tokens_for(plain.vocab, 20 + i, 20 + i) for i in range(3)}
+    for r, t in others.items():  # three requests that decode beside a long portion
+        eng.step([StepEntry(r, t[:-1], [])])
+    out = eng.step([StepEntry("long", toks[:300], list(range(300)))] + [StepEntry(r, t[-1:], [0]) for r, t in others.items()])
+    assert_rows(out.logits[:300], want[:300], "bfloat16", "a long portion beside single tokens", gaps)
+    for i, (r, t) in enumerate(others.items()):
+        assert_rows(out.logits[300 + i:301 + i], plain.logits(t)[-1:], "bfloat16", r)
+    eng.check_kernels()
+    eng32 = make_engine(folder, "float32", DEV, 16, pages=96, max_step=512)
+    assert_rows(replay_cuts(eng32, "c", toks, [200, 130, 2, 100]), want, "float32", "32-bit portions")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

@@ -85,5 +85,15 @@ PABA_5 = _model(90, 48, 4.0, 1e-5, 8.0, [
     _layer("gla", _gla(3, 24, 40, 3.0, 6), _f5),
 ])
 
-ALL = {"P1": PABA_1, "P2": PABA_2, "P3": PABA_3, "P4": PABA_4, "P5": PABA_5}
-PAGE = {"P1": 4, "P2": 8, "P3": 4, "P4": 16, "P5": 8}
+# P6: heads of 128 on pages of 16 tokens: bfloat16 steps of 128 tokens and more run the tcgen05 attention kernel
+# with the window and the sink; windows shorter and longer than a key tile, a reader of another layer's cache
+_f6 = _moe(64, 2.0, 4, 2, (32, 1.0))
+PABA_6 = _model(300, 128, 6.0, 1e-5, 12.0, [
+    _layer("attention", _att(6, 2, 128, 128, 0.09, 100, 64, 10000.0), _f6),
+    _layer("attention", _att(6, 2, 128, 128, 0.09, 200, 64, 10000.0, kv_from=0), None),
+    _layer("gla", _gla(2, 32, 64, 8.0, 8), _f6),
+    _layer("attention", _att(4, 4, 128, 128, 0.05, 37, 128, 500.0), _f6),
+])
+
+ALL = {"P1": PABA_1, "P2": PABA_2, "P3": PABA_3, "P4": PABA_4, "P5": PABA_5, "P6": PABA_6}
+PAGE = {"P1": 4, "P2": 8, "P3": 4, "P4": 16, "P5": 8, "P6": 16}

@@ -31,9 +31,8 @@ def test_splits_cover_each_tile_once(segs, group, tile, window):
         pos0 = kv_len - q_len
         hi = pos0 + tok0 + ntok
         lo = max(0, pos0 + tok0 - window + 1) if window else 0
-        kt = key_tile if key_tile is not None else (128 if tile >= 128 else 0)
-        if kt:  # kernels that fetch whole key tiles start a windowed piece on the tile that holds its first key
-            lo = lo // kt * kt
+        if tile >= 128:  # kernels that fetch whole key tiles start a windowed piece on the tile that holds its first key
+            lo = lo // 128 * 128
         parts.sort()
         assert [p[0] for p in parts] == list(range(len(parts))) and all(p[3] == len(parts) for p in parts)
         assert parts[0][1] == lo and parts[-1][2] == hi

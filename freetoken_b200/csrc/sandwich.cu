@@ -245,6 +245,67 @@ __global__ void gated_heads_kernel(const XT* __restrict__ x, int x_stride, const
   }
 }
 
+// The same for heads of 8 x 2^k elements (k <= 5) whose rows allow 16-byte accesses: a thread takes eight consecutive
+// elements, the TPR threads of a row sit side by side in a warp and add their squares by shuffles.
+template <typename XT, int TPR>
+__global__ void __launch_bounds__(256) gated_heads_vec_kernel(const XT* __restrict__ x, int x_stride,
+                                                              const __nv_bfloat16* __restrict__ g, long long g_stride,
+                                                              const float* __restrict__ norm_w, float eps, int act,
+                                                              __nv_bfloat16* __restrict__ out, int out_stride,
+                                                              int n_tokens, int n_heads) {
+  pdl_wait();
+  pdl_trigger();
+  constexpr int dim = TPR * 8;
+  const long long w = ((long long)blockIdx.x * blockDim.x + threadIdx.x) / TPR;
+  const int d = (threadIdx.x % TPR) * 8;
+  const bool ok = w < (long long)n_tokens * n_heads;
+  const long long wr = ok ? w : 0;
+  const long long t = wr / n_heads;
+  const int h = (int)(wr % n_heads);
+  float v[8], gv[8];
+  if constexpr (sizeof(XT) == 4) {
+    const float* xr = reinterpret_cast<const float*>(x) + (size_t)wr * x_stride + d;
+    const float4 a = *reinterpret_cast<const float4*>(xr), b = *reinterpret_cast<const float4*>(xr + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  } else {
+    const uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(x) + (size_t)wr * x_stride + d);
+    const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) { const float2 f = __bfloat1622float2(p2[u]); v[2 * u] = f.x; v[2 * u + 1] = f.y; }
+  }
+  {
+    const uint4 raw = *reinterpret_cast<const uint4*>(g + t * g_stride + (size_t)h * dim + d);
+    const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) { const float2 f = __bfloat1622float2(p2[u]); gv[2 * u] = f.x; gv[2 * u + 1] = f.y; }
+  }
+  float inv = 1.f;
+  if (norm_w) {
+    float ss = 0.f;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) ss += v[u] * v[u];
+#pragma unroll
+    for (int o = TPR / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    inv = rsqrtf(ss / (float)dim + eps);
+  }
+  uint4 res;
+  __nv_bfloat162* r2 = reinterpret_cast<__nv_bfloat162*>(&res);
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    float y[2];
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      const int i = 2 * u + q;
+      float val = v[i] * inv;
+      if (norm_w) val *= norm_w[d + i];
+      const float sg = 1.f / (1.f + expf(-gv[i]));
+      y[q] = val * (act == FTK_GATE_SILU ? gv[i] * sg : sg);
+    }
+    r2[u] = __floats2bfloat162_rn(y[0], y[1]);
+  }
+  if (ok) *reinterpret_cast<uint4*>(out + (size_t)w * out_stride + d) = res;
+}
+
 __global__ void softcap_kernel(float* x, long long n, float cap) {
   pdl_wait();
   pdl_trigger();
@@ -320,6 +381,26 @@ extern "C" int ftk_gated_heads(const void* x, int x_f32, int x_stride, const voi
   if (n_tokens == 0) return 0;
   FTK_REQUIRE(x && gates && out, "gated_heads: null pointer");
   const long long rows = (long long)n_tokens * n_heads;
+  const int tpr = dim / 8;
+  auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  if (dtype == FTK_BF16 && dim % 8 == 0 && tpr <= 32 && (tpr & (tpr - 1)) == 0 && x_stride % 8 == 0 && out_stride % 8 == 0 &&
+      gate_stride % 8 == 0 && al16(x) && al16(gates) && al16(out) && (!norm_w || al16(norm_w))) {
+    const long long threads = rows * tpr;
+    const unsigned blocks = (unsigned)((threads + 255) / 256);
+    const __nv_bfloat16* g = (const __nv_bfloat16*)gates;
+    __nv_bfloat16* o = (__nv_bfloat16*)out;
+#define FTK_GH(XT, N) FTK_LAUNCH((gated_heads_vec_kernel<XT, N>), blocks, 256, 0, stream, (const XT*)x, x_stride, g, gate_stride, \
+                                 norm_w, eps, act, o, out_stride, n_tokens, n_heads)
+#define FTK_GH_ALL(XT)                                                                                        \
+    (tpr == 1 ? FTK_GH(XT, 1) : tpr == 2 ? FTK_GH(XT, 2) : tpr == 4 ? FTK_GH(XT, 4) : tpr == 8 ? FTK_GH(XT, 8) \
+     : tpr == 16 ? FTK_GH(XT, 16) : FTK_GH(XT, 32))
+    if (x_f32) FTK_GH_ALL(float);
+    else FTK_GH_ALL(__nv_bfloat16);
+#undef FTK_GH_ALL
+#undef FTK_GH
+    FTK_LAUNCH_CHECK("gated_heads");
+    return 0;
+  }
   const int warps = 8;
   const unsigned blocks = (unsigned)((rows + warps - 1) / warps);
   if (dtype == FTK_F32) {

@@ -139,16 +139,17 @@ def bench_attention(a) -> dict:
     seg = torch.tensor(info, dtype=torch.int32, device=dev)
     q = torch.randn(q0, Hq, D, device=dev, generator=g).to(torch.bfloat16)
     fixed = None
-    window = int(getattr(a, "window", 0) or 0) or None  # a sliding window: the mma.sync kernels
+    window = int(getattr(a, "window", 0) or 0) or None  # a sliding window
     sink = 0.0 if getattr(a, "sink", False) else None  # a sink of logit 0 in the softmax's denominator
-    no_tc = a.no_tc or window is not None or sink is not None
+    special = window is not None or sink is not None  # of the tcgen05 kernels the one with 128-row tiles takes these
+    no_tc = a.no_tc
     tile = 128 if (a.prefill >= 128 and not no_tc and ops.attention_tc_fits(D, P, G)) else 64
-    if tile == 128 and a.pair and bias is None:
+    if tile == 128 and a.pair and bias is None and not special:
         tile = 256  # two query tiles per CTA
     few_rows = False
     if not a.prefill:
-        few_rows = a.few_rows and not no_tc and ops.attention_tc_few_fits(D, P, G)
-        tc = few_rows or (a.tc and not no_tc and ops.attention_tc_fits(D, P, G))
+        few_rows = a.few_rows and not no_tc and not special and ops.attention_tc_few_fits(D, P, G)
+        tc = few_rows or (a.tc and not no_tc and not special and ops.attention_tc_fits(D, P, G))
         fixed = wave_splits(len(segs) * Hkv, 148 if tc else 2 * 148, 16, a.context) if a.splits is None else a.splits
         tile = 16 if few_rows else 128 if tc else (16 if G <= 16 else 64)
     tensor_core = few_rows or tile >= 128  # (one CTA per SM: the engine plans these for half as many CTA slots)

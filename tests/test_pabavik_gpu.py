@@ -102,10 +102,12 @@ def test_postnorm_add_norm(dtype, H, T, k):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_gated_heads_softcap_and_scaled_embedding(dtype):
-    T, H, D, Dp = 13, 6, 24, 32
-    wide = rnd(T, 50 + H * D, dtype=dtype, seed=1)
-    gates = wide[:, 50:]
+@pytest.mark.parametrize("D,Dp,off", [(24, 32, 50), (128, 128, 64), (64, 80, 8), (8, 16, 0), (256, 256, 48), (16, 16, 3)])
+def test_gated_heads_and_softcap(dtype, D, Dp, off):
+    """Heads of 8 x 2^k elements on 16-byte rows take the kernel's form with 16-byte accesses, the others the scalar one."""
+    T, H = 13, 6
+    wide = rnd(T, off + H * D, dtype=dtype, seed=1)
+    gates = wide[:, off:]
     w = rnd(D, seed=3) + 1.0
     # a recurrent layer's 32-bit output: norm over each head, silu gate
     x32 = rnd(T, H, D, seed=2, scale=4.0)

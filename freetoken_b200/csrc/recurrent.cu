@@ -53,6 +53,14 @@ struct GlaArgs {
   int H, D, Dv, n_tokens, groups;
 };
 
+// 16 bytes from global to shared memory without a trip through registers; `valid` false writes zeros
+__device__ __forceinline__ void gla_cp16(void* dst, const void* src, bool valid) {
+  const int n = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src), "r"(n));
+}
+__device__ __forceinline__ void gla_cp_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+__device__ __forceinline__ void gla_cp_wait_all() { asm volatile("cp.async.wait_group 0;\n" ::: "memory"); }
+
 __device__ __forceinline__ float decay_of(float z, float inv_tau) {
   // sigmoid(z)^(1 / tau) = exp(-softplus(-z) / tau)
   const float sp = z > 0.f ? log1pf(expf(-z)) : -z + log1pf(expf(z));
@@ -129,9 +137,76 @@ __global__ void __launch_bounds__(gla_max_groups(DPT) * kGlaSlices * 32) gla_chu
   const bool wide = sizeof(T) == 2 && D % 8 == 0 && a.q_stride % 8 == 0 && a.k_stride % 8 == 0 &&
                     ((reinterpret_cast<uintptr_t>(a.q) | reinterpret_cast<uintptr_t>(a.k) |
                       reinterpret_cast<uintptr_t>(a.z)) & 15) == 0;
+  // bfloat16 rows that allow it are fetched a batch ahead: cp.async brings the next 16 tokens' q, k, decay logits and
+  // values as they lie in memory into a second set of buffers while the current 16 are worked on, and a pass
+  // from shared to shared memory widens them
+  // (a chunk of one batch has nothing to fetch ahead of: it takes the direct way)
+  const bool ahead = wide && ntok > kGlaBatch && Dv % 8 == 0 && a.v_stride % 8 == 0 && (reinterpret_cast<uintptr_t>(a.v) & 15) == 0;
+  __nv_bfloat16* kraw = reinterpret_cast<__nv_bfloat16*>(part + kGlaSlices * kGlaBatch * cols);  // [batch][Dp]
+  __nv_bfloat16* qraw = kraw + kGlaBatch * Dp;
+  float* zraw = reinterpret_cast<float*>(qraw + kGlaBatch * Dp);                                  // [batch][Dp]
+  __nv_bfloat16* vraw = reinterpret_cast<__nv_bfloat16*>(zraw + kGlaBatch * Dp);                  // [batch][cols]
+  auto fetch = [&](int b0n) {
+    const int nbn = min(kGlaBatch, ntok - b0n);
+    const int per_row = Dp / 8;
+    const __nv_bfloat16* kg = reinterpret_cast<const __nv_bfloat16*>(a.k);
+    const __nv_bfloat16* qg = reinterpret_cast<const __nv_bfloat16*>(a.q);
+    const __nv_bfloat16* vg = reinterpret_cast<const __nv_bfloat16*>(a.v);
+    for (int i = threadIdx.x; i < nbn * per_row; i += blockDim.x) {
+      const int t = i / per_row, d = (i % per_row) * 8;
+      const size_t tok = (size_t)(q_start + tok0 + b0n + t);
+      const bool in = d < D;
+      gla_cp16(kraw + t * Dp + d, in ? kg + tok * a.k_stride + (size_t)h * D + d : kg, in);
+      if (MODE != 1) gla_cp16(qraw + t * Dp + d, in ? qg + tok * a.q_stride + (size_t)h * D + d : qg, in);
+      const float* zr = in ? a.z + (tok * a.H + h) * D + d : a.z;
+      gla_cp16(zraw + t * Dp + d, zr, in);
+      gla_cp16(zraw + t * Dp + d + 4, in ? zr + 4 : zr, in);
+    }
+    const int vper = cols / 8;
+    for (int i = threadIdx.x; i < nbn * vper; i += blockDim.x) {
+      const int t = i / vper, j = (i % vper) * 8;
+      const size_t tok = (size_t)(q_start + tok0 + b0n + t);
+      const bool in = col0 + j < Dv;
+      gla_cp16(vraw + t * cols + j, in ? vg + tok * a.v_stride + (size_t)h * Dv + col0 + j : vg, in);
+    }
+    gla_cp_commit();
+  };
+  if (sizeof(T) == 2 && ahead) fetch(0);
   for (int b0 = 0; b0 < ntok; b0 += kGlaBatch) {
     const int nb = min(kGlaBatch, ntok - b0);
+    if (sizeof(T) == 2 && ahead) gla_cp_wait_all();
     __syncthreads();
+    if (sizeof(T) == 2 && ahead) {
+      for (int i = threadIdx.x * 4; i < nb * Dp; i += blockDim.x * 4) {
+        const int d = i % Dp;
+        const __nv_bfloat162* k2 = reinterpret_cast<const __nv_bfloat162*>(kraw + i);
+        const float2 k01 = __bfloat1622float2(k2[0]), k23 = __bfloat1622float2(k2[1]);
+        *reinterpret_cast<float4*>(sk + i) = make_float4(k01.x, k01.y, k23.x, k23.y);
+        if (MODE != 1) {
+          const __nv_bfloat162* q2 = reinterpret_cast<const __nv_bfloat162*>(qraw + i);
+          const float2 q01 = __bfloat1622float2(q2[0]), q23 = __bfloat1622float2(q2[1]);
+          *reinterpret_cast<float4*>(sq + i) = make_float4(q01.x * a.q_scale, q01.y * a.q_scale, q23.x * a.q_scale, q23.y * a.q_scale);
+        }
+        float4 av = *reinterpret_cast<const float4*>(zraw + i);
+        if (d >= D) {
+          av = make_float4(1.f, 1.f, 1.f, 1.f);
+        } else if (!a.z_is_decay) {
+          const float* bz = a.z_bias ? a.z_bias + (size_t)h * D + d : nullptr;
+          av.x = decay_of(av.x + (bz ? bz[0] : 0.f), a.inv_tau);
+          av.y = decay_of(av.y + (bz ? bz[1] : 0.f), a.inv_tau);
+          av.z = decay_of(av.z + (bz ? bz[2] : 0.f), a.inv_tau);
+          av.w = decay_of(av.w + (bz ? bz[3] : 0.f), a.inv_tau);
+        }
+        *reinterpret_cast<float4*>(sa + i) = av;
+      }
+      for (int i = threadIdx.x * 2; i < nb * cols; i += blockDim.x * 2) {
+        const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(vraw + i));
+        sv[i] = f.x;
+        sv[i + 1] = f.y;
+      }
+      __syncthreads();
+      if (b0 + kGlaBatch < ntok) fetch(b0 + kGlaBatch);  // the buffers are read: the next batch may land
+    } else {
     if (wide) {
       const int per_row = Dp / 8;
       for (int i = threadIdx.x; i < nb * per_row; i += blockDim.x) {
@@ -187,6 +262,7 @@ __global__ void __launch_bounds__(gla_max_groups(DPT) * kGlaSlices * 32) gla_chu
       sv[i] = col0 + j < Dv ? to_float(vb[tok * a.v_stride + (size_t)h * Dv + col0 + j]) : 0.f;
     }
     __syncthreads();
+    }
     for (int t = 0; t < nb; ++t) {
       float vj[NC], acc[NC][4];  // four chains per column, added in a fixed order
 #pragma unroll
@@ -287,8 +363,10 @@ static int launch_gla(GlaArgs a, bool any_single, bool any_multi, cudaStream_t s
   a.groups = min(tiles, gla_max_groups(DPT));
   const int cols = a.groups * kGlaCols;
   const int threads = a.groups * kGlaSlices * 32;
-  const size_t smem = ((size_t)3 * kGlaBatch * Dp + (size_t)kGlaBatch * cols + (size_t)kGlaSlices * kGlaBatch * cols) *
-                      sizeof(float);
+  size_t smem = ((size_t)3 * kGlaBatch * Dp + (size_t)kGlaBatch * cols + (size_t)kGlaSlices * kGlaBatch * cols) *
+                sizeof(float);
+  if (sizeof(T) == 2)  // the next batch as it lies in memory: q, k (bfloat16), decay logits (float), values (bfloat16)
+    smem += (size_t)kGlaBatch * Dp * (2 + 2 + 4) + (size_t)kGlaBatch * cols * 2;
   dim3 grid(a.n_chunks, a.H, (a.Dv + cols - 1) / cols);
   auto k0 = gla_chunk_kernel<T, DPT, 0>;
   auto k1 = gla_chunk_kernel<T, DPT, 1>;

@@ -23,7 +23,7 @@ import sys
 from typing import List, Optional
 
 PAGE_SIZE = 16  # divides 64: a request's pages never exceed its token count rounded up to 64
-MAX_LIVE = 8
+MAX_LIVE = 4  # requests live at any time: the engine gets that many request rows and state slots, so slots are used again
 
 
 def build_parser() -> argparse.ArgumentParser:

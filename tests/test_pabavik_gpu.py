@@ -3,7 +3,6 @@ a sink left out, a window one token off or a lost state shows, and the engine (3
 plain model (tests/plain/pabavik_plain.py) under every way of cutting and batching the work."""
 
 import json
-import math
 import os
 import subprocess
 import sys
